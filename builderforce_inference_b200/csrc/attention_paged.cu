@@ -6,6 +6,8 @@
 // Reference formula (crates/bfi-core/src/cpu.rs:328-392): score = q.k / sqrt(d) for keys at or
 // before the query's position, softmax over them, weighted sum of V; query head h reads kv head
 // h / (n_q / n_kv).  `window` > 0 keeps only the last `window` keys (pos - window < j <= pos).
+// `has_sink`: the softmax's denominator carries one more term, exp(sink), a score that every
+// query sees and that has no value: p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)).
 //
 // Work split: one block per (sequence, kv head, chunk of heads of its group, chunk of tokens);
 // 16 query rows per block (GH heads x 16/GH consecutive tokens) share each tile of 32 keys that
@@ -25,7 +27,7 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv, int d,
-                       int gh, int head_chunks, int window, float scale) {
+                       int gh, int head_chunks, int window, float scale, int has_sink, float sink) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -145,7 +147,9 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
         const int r = warp * 2 + i;
         const int tok = tok0 + r / gh;
         const int hl = hc * gh + r % gh;
-        const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+        float l = l_run[i];
+        if (has_sink && m_run[i] > -INFINITY) l += expf(sink - m_run[i]);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         T* o = out + (size_t)(t0 + tok) * out_stride + (size_t)(kvh * group + hl) * d;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
@@ -159,7 +163,7 @@ template <typename T, int NC>
 static int launch_attention(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                             const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                             const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv,
-                            int d, int window, float scale, cudaStream_t stream) {
+                            int d, int window, float scale, int has_sink, float sink, cudaStream_t stream) {
     const int group = n_q / n_kv;
     int gh = 1;
     while (gh < group && gh < 8) gh *= 2;
@@ -177,7 +181,7 @@ static int launch_attention(const void* q, long q_stride, void* out, long out_st
     }
     bfi_launch(kernel, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,
                                                    (const T*)v_pages, block_table, table_stride, cu_seqlens, seq_slot,
-                                                   seq_start, n_q, n_kv, d, gh, head_chunks, window, scale);
+                                                   seq_start, n_q, n_kv, d, gh, head_chunks, window, scale, has_sink, sink);
     return bfi_check_launch("attention_paged");
 }
 
@@ -185,12 +189,12 @@ template <typename T>
 static int dispatch_nc(int nc, const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                        const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                        const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv, int d,
-                       int window, float scale, cudaStream_t stream) {
+                       int window, float scale, int has_sink, float sink, cudaStream_t stream) {
 #define BFI_ATT_CASE(N)                                                                                              \
     case N:                                                                                                          \
         return launch_attention<T, N>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,     \
                                       cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window,     \
-                                      scale, stream);
+                                      scale, has_sink, sink, stream);
     switch (nc) {
         BFI_ATT_CASE(1)
         BFI_ATT_CASE(2)
@@ -209,12 +213,12 @@ static int dispatch_nc(int nc, const void* q, long q_stride, void* out, long out
 extern "C" int bfi_attention_paged(const void* q, int dtype, long q_stride, void* out, long out_stride,
                                    const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                                    const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
-                                   int max_tokens, int n_q, int n_kv, int d, int window, float scale,
-                                   cudaStream_t stream) {
+                                   int max_tokens, int n_q, int n_kv, int d, int window, float scale, int has_sink,
+                                   float sink, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "attention_paged: unknown dtype code %d", dtype);
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_paged: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
-    BFI_REQUIRE(d > 0 && d % 16 == 0 && d <= ATT_MAX_D, "attention_paged: head_dim %d must be a multiple of 16, at most %d",
+    BFI_REQUIRE(d > 0 && d % 2 == 0 && d <= ATT_MAX_D, "attention_paged: head_dim %d must be even, at most %d",
                 d, ATT_MAX_D);
     BFI_REQUIRE(window >= 0, "attention_paged: negative window");
     BFI_REQUIRE(q_stride >= (long)n_q * d && out_stride >= (long)n_q * d, "attention_paged: token stride shorter than the heads");
@@ -226,7 +230,7 @@ extern "C" int bfi_attention_paged(const void* q, int dtype, long q_stride, void
     if (nc > 8) nc = 16;
     if (dtype == BFI_F32)
         return dispatch_nc<float>(nc, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
-                                  cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, stream);
+                                  cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, has_sink, sink, stream);
     return dispatch_nc<bf16>(nc, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                             seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, stream);
+                             seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, has_sink, sink, stream);
 }

@@ -11,11 +11,11 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :]   (out is the float32 residual stream)
+// embedding: out[t, :] = table[ids[t], :] * scale   (out is the float32 residual stream)
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                  float* __restrict__ out, int width, int vocab, int* status) {
+                                  float* __restrict__ out, int width, int vocab, float scale, int* status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -27,20 +27,20 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
         return;
     }
     const T* row = table + (size_t)id * width;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = to_f32(row[j]);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = to_f32(row[j]) * scale;
 }
 
 extern "C" int bfi_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
-                              int n_tokens, int width, int vocab, int* status, cudaStream_t stream) {
+                              int n_tokens, int width, int vocab, float scale, int* status, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(table_dtype), "embed_rows: unknown table dtype code %d", table_dtype);
     BFI_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes tokens=%d width=%d vocab=%d",
                 n_tokens, width, vocab);
     if (n_tokens == 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == BFI_F32)
-        bfi_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width, vocab, status);
+        bfi_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width, vocab, scale, status);
     else
-        bfi_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, width, vocab, status);
+        bfi_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, width, vocab, scale, status);
     return bfi_check_launch("embed_rows");
 }
 
@@ -204,6 +204,59 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, long in_stride, T* __r
         const float u = to_f32(interleaved ? row[2 * j + 1] : row[inter + j]);
         out[r * out_stride + j] = from_f32<T>(silu_f32(g) * u);
     }
+}
+
+// The gated activation in its general form, for gate/up pairs as above:
+//     g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(alpha * g') * (u' + shift)
+// (limit <= 0: no clamping).  alpha 1, no limit and shift 0 is SiLU(gate) * up.
+__device__ __forceinline__ float gate_mul_f32(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    const float z = alpha * g;
+    float s;
+    if (z >= 0.0f) {
+        s = 1.0f / (1.0f + expf(-z));
+    } else {
+        const float e = expf(z);
+        s = e / (1.0f + e);
+    }
+    return g * s * (u + shift);
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ gu, long in_stride, T* __restrict__ out, long out_stride,
+                                int n_rows, int inter, int interleaved, float alpha, float limit, float shift) {
+    pdl_trigger();
+    pdl_wait();
+    const long total = (long)n_rows * inter;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / inter;
+        const int j = (int)(i - r * inter);
+        const T* row = gu + r * in_stride;
+        const float g = to_f32(interleaved ? row[2 * j] : row[j]);
+        const float u = to_f32(interleaved ? row[2 * j + 1] : row[inter + j]);
+        out[r * out_stride + j] = from_f32<T>(gate_mul_f32(g, u, alpha, limit, shift));
+    }
+}
+
+extern "C" int bfi_gate_mul(const void* gu, long in_stride, void* out, long out_stride, int dtype, int n_rows, int inter,
+                            int interleaved, float alpha, float limit, float shift, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype), "gate_mul: unknown dtype code %d", dtype);
+    BFI_REQUIRE(n_rows >= 0 && inter > 0, "gate_mul: bad sizes rows=%d width=%d", n_rows, inter);
+    BFI_REQUIRE(in_stride >= 2L * inter && out_stride >= inter, "gate_mul: row stride shorter than the row");
+    if (n_rows == 0) return 0;
+    const long total = (long)n_rows * inter;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < bfi_sm_count() * 16L ? (total + threads - 1) / threads : bfi_sm_count() * 16L);
+    if (dtype == BFI_F32)
+        bfi_launch(gate_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, in_stride, (float*)out, out_stride,
+                   n_rows, inter, interleaved, alpha, limit, shift);
+    else
+        bfi_launch(gate_mul_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gu, in_stride, (bf16*)out, out_stride,
+                   n_rows, inter, interleaved, alpha, limit, shift);
+    return bfi_check_launch("gate_mul");
 }
 
 extern "C" int bfi_silu_mul(const void* gu, long in_stride, void* out, long out_stride, int dtype, int n_rows,

@@ -134,7 +134,7 @@ class Decoder:
     # ---- compute ---------------------------------------------------------------------
     def embed(self, ctx) -> torch.Tensor:
         x = ctx.rows("residual", self.spec.width, torch.float32)
-        ops.embed_rows(self.embedding, ctx.token_ids[:ctx.n_tokens], x, ctx.status)
+        ops.embed_rows(self.embedding, ctx.token_ids[:ctx.n_tokens], x, ctx.status, float(self.spec.embedding_scale))
         return x
 
     def run_layers(self, ctx, x: torch.Tensor, cache, first: int = 0, last: Optional[int] = None) -> None:

@@ -5,8 +5,10 @@ from __future__ import annotations
 import torch
 
 
-def attend(ctx, qkv, out, kv, n_heads: int, scale: float) -> bool:
+def attend(ctx, qkv, out, kv, n_heads: int, scale: float, sink=None) -> bool:
     if qkv.dtype != torch.bfloat16:
+        return False
+    if sink is not None:
         return False
     from . import fast_ops
     if ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs:

@@ -76,7 +76,8 @@ def convert(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 
 def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
-               status: Optional[torch.Tensor] = None) -> None:
+               status: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """``out[t] = table[ids[t]] * scale`` into the float32 residual stream."""
     _need_cuda(table, ids, out, status)
     _rows_2d(table, "embedding table")
     _rows_2d(out, "embedding output")
@@ -86,7 +87,8 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
     if not table.is_contiguous():
         raise KernelError("embedding table must be contiguous")
     library("core").call("bfi_embed_rows", _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out),
-                         c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]), _ptr(status), _stream())
+                         c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]), c_float(scale), _ptr(status),
+                         _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
@@ -116,6 +118,20 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, interleaved: bool) -> None:
     library("core").call("bfi_silu_mul", _ptr(gu), c_long(gu.stride(0)), _ptr(out), c_long(out.stride(0)),
                          c_int(dtype_code(gu.dtype)), c_int(gu.shape[0]), c_int(out.shape[1]),
                          c_int(1 if interleaved else 0), _stream())
+
+
+def gate_mul(gu: torch.Tensor, out: torch.Tensor, interleaved: bool, alpha: float = 1.0, limit: float = 0.0,
+             shift: float = 0.0) -> None:
+    """The gated activation over gate/up pairs: ``g' * sigmoid(alpha * g') * (u' + shift)`` with
+    ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)`` (``limit`` 0: no clamping)."""
+    _need_cuda(gu, out)
+    _rows_2d(gu, "gate/up input")
+    _rows_2d(out, "gated output")
+    if gu.dtype != out.dtype or gu.shape[0] != out.shape[0] or gu.shape[1] != 2 * out.shape[1]:
+        raise KernelError("gate_mul: input must be [rows, 2*width] and output [rows, width] of one dtype")
+    library("core").call("bfi_gate_mul", _ptr(gu), c_long(gu.stride(0)), _ptr(out), c_long(out.stride(0)),
+                         c_int(dtype_code(gu.dtype)), c_int(gu.shape[0]), c_int(out.shape[1]),
+                         c_int(1 if interleaved else 0), c_float(alpha), c_float(limit), c_float(shift), _stream())
 
 
 def residual_add(x: torch.Tensor, y: torch.Tensor) -> None:
@@ -169,11 +185,126 @@ def qk_norm_rope_cache(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
         _ptr(v_pages), _ptr(table), c_int(stride), c_int(flags), _ptr(status), _stream())
 
 
+NORM_NONE, NORM_HEAD, NORM_ROW = 0, 1, 2
+PAIR_HALF, PAIR_ADJACENT = 0, 1
+FLAG_VALUES_ARE_KEYS = 4
+
+
+def qk_prepare(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, token_pos: torch.Tensor,
+               token_slot: torch.Tensor, kv, flags: int, *, q_bias=None, k_bias=None, v_bias=None,
+               q_norm_w=None, k_norm_w=None, norm_mode: int = NORM_NONE, eps: float = 1e-6, rope_table=None,
+               rot_dim: int = 0, pairing: int = PAIR_HALF, residual=None, out_bias=None,
+               status: Optional[torch.Tensor] = None) -> None:
+    """Between the q/k(/v) projection and the attention, one block per token: biases, the values
+    (the row's own v heads, or with ``FLAG_VALUES_ARE_KEYS`` the keys as they stand after their
+    bias), a norm per head or over the whole projection, the rotation with either pairing, q back in
+    place and k, v into the cache; ``out_bias`` is added to the token's row of ``residual``."""
+    _need_cuda(qkv, q_bias, k_bias, v_bias, q_norm_w, k_norm_w, rope_table, token_pos, token_slot, residual, out_bias, status)
+    _rows_2d(qkv, "qkv")
+    _i32(token_pos, "token positions")
+    _i32(token_slot, "token slots")
+    n_tokens = qkv.shape[0]
+    own_v = not (flags & FLAG_VALUES_ARE_KEYS)
+    if token_pos.numel() < n_tokens or token_slot.numel() < n_tokens:
+        raise KernelError("qk_prepare: position/slot arrays shorter than the tokens")
+    if qkv.shape[1] != (n_q + (2 if own_v else 1) * n_kv) * head_dim:
+        raise KernelError(f"qk_prepare: a row of {qkv.shape[1]} values does not hold the heads")
+    bias_dt = norm_dt = 0
+    for b, n in ((q_bias, n_q), (k_bias, n_kv), (v_bias, n_kv)):
+        if b is not None:
+            if b.shape != (n * head_dim,) or not b.is_contiguous():
+                raise KernelError(f"qk_prepare: a projection bias must be [{n * head_dim}]")
+            bias_dt = dtype_code(b.dtype)
+    if len({b.dtype for b in (q_bias, k_bias, v_bias) if b is not None}) > 1:
+        raise KernelError("qk_prepare: the projection biases must share a dtype")
+    for w, n in ((q_norm_w, n_q), (k_norm_w, n_kv)):
+        if w is not None:
+            want = head_dim if norm_mode == NORM_HEAD else n * head_dim
+            if w.shape != (want,) or not w.is_contiguous():
+                raise KernelError(f"qk_prepare: norm weight must be [{want}], got {tuple(w.shape)}")
+            norm_dt = dtype_code(w.dtype)
+    if q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype:
+        raise KernelError("q and k norm weights must share a dtype")
+    positions = 0
+    if rope_table is not None:
+        if rope_table.dtype != torch.float32 or not rope_table.is_contiguous() or rope_table.dim() != 3 \
+                or rope_table.shape[1] != rot_dim // 2 or rope_table.shape[2] != 2:
+            raise KernelError("rotation table must be contiguous float32 [positions, rot_dim/2, 2]")
+        positions = rope_table.shape[0]
+    k_pages = v_pages = table = None
+    stride = 0
+    if kv is not None and (flags & FLAG_WRITE_CACHE):
+        if kv.k.dtype != qkv.dtype or kv.n_kv_heads != n_kv or kv.head_dim != head_dim:
+            raise KernelError("cache pages do not fit the heads being written")
+        k_pages, v_pages, table = kv.k, kv.v, kv.block_table
+        stride = table.stride(0)
+    width = r_stride = ob_dt = 0
+    if out_bias is not None:
+        if residual is None or residual.dtype != torch.float32 or residual.dim() != 2 or residual.stride(1) != 1 \
+                or residual.shape[0] < n_tokens or out_bias.shape != (residual.shape[1],) or not out_bias.is_contiguous():
+            raise KernelError("qk_prepare: the output bias needs the float32 residual [tokens, width] and a bias [width]")
+        width, r_stride, ob_dt = residual.shape[1], residual.stride(0), dtype_code(out_bias.dtype)
+    library("core").call(
+        "bfi_qk_prepare", _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_long(qkv.stride(0)), c_int(n_tokens), c_int(n_q),
+        c_int(n_kv), c_int(head_dim), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), c_int(bias_dt), _ptr(q_norm_w),
+        _ptr(k_norm_w), c_int(norm_dt), c_int(norm_mode), c_float(eps), _ptr(rope_table), c_int(rot_dim),
+        c_int(positions), c_int(pairing), _ptr(token_pos), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages), _ptr(table),
+        c_int(stride), c_int(flags), _ptr(residual if out_bias is not None else None), c_long(r_stride), _ptr(out_bias),
+        c_int(ob_dt), c_int(width), _ptr(status), _stream())
+
+
+LIGHT_ACT_NONE, LIGHT_ACT_SILU = 0, 1
+
+
+def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
+                   decay: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+                   n_heads: int, dim: int, vdim: int, act: int = LIGHT_ACT_SILU, few_tokens: bool = False) -> None:
+    """Linear attention with a decay per head over the step's new tokens, sequence by sequence:
+    ``S = decay * S + k v^T; o = S^T q`` with ``S`` float32 ``[slots, heads, dim, vdim]`` carried
+    in ``state``.  q, k, v are columns ``q_off``, ``k_off``, ``v_off`` of ``proj`` (activated here
+    when ``act`` says so); ``out`` is float32 ``[tokens, heads * vdim]``."""
+    _need_cuda(proj, out, state, decay, cu_seqlens, seq_slot)
+    _rows_2d(proj, "projections")
+    _rows_2d(out, "recurrence output")
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(seq_slot, "sequence slots")
+    if out.dtype != torch.float32 or out.shape[1] != n_heads * vdim:
+        raise KernelError("lightning_scan: the output must be float32 [tokens, heads * vdim]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
+        raise KernelError("lightning_scan: the state must be contiguous float32 [slots, heads, dim, vdim]")
+    if decay.dtype != torch.float32 or not decay.is_contiguous() or decay.numel() != n_heads:
+        raise KernelError("lightning_scan: one float32 decay per head")
+    if max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * vdim > proj.shape[1]:
+        raise KernelError("lightning_scan: the projections' row is shorter than the heads")
+    library("core").call("bfi_lightning_scan", _ptr(proj), c_int(dtype_code(proj.dtype)), c_long(proj.stride(0)),
+                         c_int(q_off), c_int(k_off), c_int(v_off), _ptr(out), c_long(out.stride(0)), _ptr(state),
+                         _ptr(decay), _ptr(cu_seqlens), _ptr(seq_slot), c_int(n_seqs), c_int(n_heads), c_int(dim),
+                         c_int(vdim), c_int(act), c_int(1 if few_tokens else 0), _stream())
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = x * rsqrt(mean(x^2) + eps) * w * sigmoid(gate)`` row by row; ``x`` float32, ``gate``
+    (a view into the projections) and ``out`` in the activation dtype."""
+    _need_cuda(x, gate, w, out)
+    _rows_2d(x, "norm input")
+    _rows_2d(gate, "gate")
+    _rows_2d(out, "norm output")
+    n, width = x.shape
+    if x.dtype != torch.float32 or gate.dtype != out.dtype or gate.shape != (n, width) or out.shape != (n, width):
+        raise KernelError("gated_rmsnorm: x float32 [rows, width]; gate and output [rows, width] of one dtype")
+    if w.shape != (width,) or not w.is_contiguous():
+        raise KernelError(f"gated_rmsnorm: weight must be [{width}]")
+    library("core").call("bfi_gated_rmsnorm", _ptr(x), c_long(x.stride(0)), _ptr(gate), c_long(gate.stride(0)),
+                         c_int(dtype_code(out.dtype)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(out),
+                         c_long(out.stride(0)), c_int(n), c_int(width), c_float(eps), _stream())
+
+
 def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_seqlens: torch.Tensor,
                     seq_slot: torch.Tensor, seq_start: torch.Tensor, n_seqs: int, max_tokens: int,
-                    n_q: int, scale: float) -> None:
+                    n_q: int, scale: float, sink: Optional[float] = None) -> None:
     """``q`` is the first query element of the step (a view into the qkv buffer); token ``t``, head
-    ``h`` lies at ``q + t*q_stride + h*head_dim``.  ``out`` is ``[tokens, n_q*head_dim]``."""
+    ``h`` lies at ``q + t*q_stride + h*head_dim``.  ``out`` is ``[tokens, n_q*head_dim]``.  With
+    ``sink`` the softmax's denominator carries ``exp(sink)`` beside the keys' terms."""
     _need_cuda(q, out, cu_seqlens, seq_slot, seq_start)
     _rows_2d(out, "attention output")
     _i32(cu_seqlens, "cu_seqlens")
@@ -185,7 +316,8 @@ def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_se
         "bfi_attention_paged", _ptr(q), c_int(dtype_code(q.dtype)), c_long(q_stride), _ptr(out),
         c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)),
         _ptr(cu_seqlens), _ptr(seq_slot), _ptr(seq_start), c_int(n_seqs), c_int(max_tokens), c_int(n_q),
-        c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(kv.window or 0), c_float(scale), _stream())
+        c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(kv.window or 0), c_float(scale),
+        c_int(0 if sink is None else 1), c_float(0.0 if sink is None else sink), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:

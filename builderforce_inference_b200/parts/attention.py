@@ -9,6 +9,16 @@ The three projections are one matrix product over the concatenated weights.  Key
 are always read from the cache, so a step may bring whole prompts, a continuation of a cached
 prefix, or single tokens, and a run may read another run's cache (``run.writes_cache`` false:
 this layer then has no k and v projections of its own).
+
+Variants, each a parameter: ``bias`` (q, k, v and output projections carry one); ``qk_norm``
+``"head"`` (RMS norm over each head, one weight of ``head_dim``) or ``"row"`` (RMS norm over the
+whole q projection and over the whole k projection, weights of that size); ``values`` ``"keys"``
+(no v projection: the values are the keys as projected, with their bias, before norm and
+rotation); ``sink`` (a score every query sees beside its keys, with no value: the softmax's
+denominator carries ``exp(sink)``); the position encoding's pairing and partial width.  The plain
+combination (no bias, head norm or none, own values, rotate-half) runs the per-head kernel that
+fuses norm, rotation and cache write; the others run the per-token kernel that also adds the
+biases, so no variant costs a launch of its own.
 """
 from __future__ import annotations
 
@@ -27,21 +37,33 @@ class Attention(Mixer):
     graph_safe = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                 position: Optional[PartSpec] = None, qk_norm: bool = False, eps: float = 1e-6,
-                 window: Optional[int] = None, scale: Optional[float] = None, own_kv: bool = True):
+                 position: Optional[PartSpec] = None, qk_norm=False, eps: float = 1e-6,
+                 window: Optional[int] = None, scale: Optional[float] = None, own_kv: bool = True,
+                 bias: bool = False, values: str = "projection", sink: Optional[float] = None):
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"GQA: {n_heads} query heads do not divide into {n_kv_heads} kv heads")
-        if head_dim % 16 != 0 or head_dim > 512:
-            raise ValueError(f"attention kernels take head sizes in steps of 16 up to 512, got {head_dim}")
+        if head_dim % 2 != 0 or head_dim > 512:
+            raise ValueError(f"attention kernels take even head sizes up to 512, got {head_dim}")
+        if qk_norm is True:
+            qk_norm = "head"
+        if qk_norm not in (False, None, "head", "row"):
+            raise ValueError(f"qk_norm must be false, 'head' or 'row', got {qk_norm!r}")
+        if values not in ("projection", "keys"):
+            raise ValueError(f"values must be 'projection' or 'keys', got {values!r}")
+        if values == "keys" and not own_kv:
+            raise ValueError("a layer without keys of its own has no keys to use as values")
         if window is not None and window < 1:
             raise ValueError(f"window must be positive, got {window}")
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
-        self.qk_norm, self.eps, self.window = bool(qk_norm), float(eps), window
+        self.qk_norm, self.eps, self.window = (qk_norm or None), float(eps), window
+        self.bias, self.values_are_keys = bool(bias), values == "keys"
+        self.sink = None if sink is None else float(sink)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.own_kv = bool(own_kv)
         self.position = POSITION_ENCODINGS.build(position) if position is not None \
             else POSITION_ENCODINGS.build(PartSpec("none"))
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.b_q = self.b_k = self.b_v = self.b_o = None
 
     def children(self):
         return {"position": self.position}
@@ -51,12 +73,23 @@ class Attention(Mixer):
         specs = {"q_proj": ParamSpec((self.n_heads * d, h)), "o_proj": ParamSpec((h, self.n_heads * d))}
         if self.own_kv:
             specs["k_proj"] = ParamSpec((self.n_kv_heads * d, h))
-            specs["v_proj"] = ParamSpec((self.n_kv_heads * d, h))
+            if not self.values_are_keys:
+                specs["v_proj"] = ParamSpec((self.n_kv_heads * d, h))
         if self.qk_norm:
-            specs["q_norm"] = ParamSpec((d,), "norm")
+            row = self.qk_norm == "row"
+            specs["q_norm"] = ParamSpec((self.n_heads * d if row else d,), "norm")
             if self.own_kv:
-                specs["k_norm"] = ParamSpec((d,), "norm")
+                specs["k_norm"] = ParamSpec((self.n_kv_heads * d if row else d,), "norm")
+        if self.bias:
+            for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                if name in specs:
+                    specs[name + ".bias"] = ParamSpec((specs[name].shape[0],), "matrix")
         return specs
+
+    def _plain(self) -> bool:
+        """The combination the per-head kernel (norm, rotate-half, cache write) covers."""
+        return not self.bias and not self.values_are_keys and self.qk_norm != "row" \
+            and getattr(self.position, "pairing", "half") == "half"
 
     def cache_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window)
@@ -67,7 +100,7 @@ class Attention(Mixer):
     def load(self, tensors, runtime) -> None:
         mats = [tensors["q_proj"]]
         if self.own_kv:
-            mats += [tensors["k_proj"], tensors["v_proj"]]
+            mats += [tensors["k_proj"]] + ([] if self.values_are_keys else [tensors["v_proj"]])
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
         self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
@@ -76,6 +109,11 @@ class Attention(Mixer):
         self.k_norm = tensors.get("k_norm")
         if self.q_norm is not None and self.k_norm is not None and self.q_norm.dtype != self.k_norm.dtype:
             self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+        if self.bias:
+            self.b_q, self.b_k, self.b_v = (tensors.get(n + ".bias") for n in ("q_proj", "k_proj", "v_proj"))
+            self.b_o = tensors["o_proj.bias"]
+            if len({b.dtype for b in (self.b_q, self.b_k, self.b_v) if b is not None}) > 1:
+                self.b_q, self.b_k, self.b_v = (None if b is None else b.float() for b in (self.b_q, self.b_k, self.b_v))
 
     def forward(self, ctx, h, residual, run) -> None:
         kv = run.kv
@@ -85,12 +123,23 @@ class Attention(Mixer):
         if run.writes_cache != self.own_kv:
             raise RuntimeError("an attention layer writes the cache exactly when it has k and v projections")
         d = self.head_dim
-        qkv = ctx.rows("attn.qkv", (self.n_heads + 2 * n_kv_in) * d)
+        qkv = ctx.rows("attn.qkv", (self.n_heads + (1 if self.values_are_keys else 2) * n_kv_in) * d)
         linear(h, self.w_qkv, qkv, EPI_STORE)
 
         fused = self.position.fused_rotary()
         write = ops.FLAG_WRITE_CACHE if run.writes_cache else 0
-        if fused is not None:
+        if not self._plain():
+            if fused is None:
+                raise RuntimeError("this attention variant needs a position encoding the kernels apply themselves")
+            table, rot = fused
+            ops.qk_prepare(qkv, self.n_heads, n_kv_in, d, ctx.token_pos, ctx.token_slot, kv,
+                           write | (ops.FLAG_VALUES_ARE_KEYS if self.values_are_keys else 0),
+                           q_bias=self.b_q, k_bias=self.b_k, v_bias=self.b_v, q_norm_w=self.q_norm, k_norm_w=self.k_norm,
+                           norm_mode={None: ops.NORM_NONE, "head": ops.NORM_HEAD, "row": ops.NORM_ROW}[self.qk_norm],
+                           eps=self.eps, rope_table=table, rot_dim=rot,
+                           pairing=ops.PAIR_ADJACENT if getattr(self.position, "pairing", "half") == "adjacent" else ops.PAIR_HALF,
+                           residual=residual, out_bias=self.b_o, status=ctx.status)
+        elif fused is not None:
             table, rot = fused
             ops.qk_norm_rope_cache(qkv, self.n_heads, n_kv_in, d, self.q_norm, self.k_norm, self.eps,
                                    table, rot, ctx.token_pos, ctx.token_slot, kv, write, ctx.status)
@@ -111,7 +160,7 @@ class Attention(Mixer):
 
     def attend(self, ctx, qkv, out, kv) -> None:
         from ..kernels import attention as fast_attention
-        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale):
+        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale, self.sink):
             return
         ops.attention_paged(qkv, qkv.stride(0), out, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
-                            ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale)
+                            ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, self.sink)

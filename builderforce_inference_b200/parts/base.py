@@ -218,3 +218,4 @@ class ModelSpec:
     ignored_names: Sequence[str] = ()  # tensors a checkpoint may carry that are not used
     max_positions: int = 0
     stop_ids: Tuple[int, ...] = ()
+    embedding_scale: float = 1.0       # the embedding rows are multiplied by it; the tied head is not

@@ -4,6 +4,11 @@
 The gate and up matrices are stored interleaved row by row (gate_j, up_j, gate_j+1, ...), so
 one matrix product yields both and its epilogue applies SiLU*mul while the pair is still in
 registers; the down product adds into the residual stream.
+
+The activation is a family with three constants: with ``g' = min(g, limit)`` and
+``u' = clamp(u, -limit, limit)`` (no clamping without a limit),
+``act = g' * sigmoid(gate_alpha * g') * (u' + up_shift)``.  ``gate_alpha`` 1, no limit and
+``up_shift`` 0 is SiLU(gate) * up.
 """
 from __future__ import annotations
 
@@ -11,7 +16,8 @@ from typing import Dict
 
 import torch
 
-from ..kernels.linear import EPI_ACCUMULATE, EPI_SWIGLU, linear
+from ..kernels import ops
+from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, EPI_SWIGLU, linear
 from .base import FEED_FORWARDS, FeedForward, ParamSpec
 
 
@@ -19,10 +25,15 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    def __init__(self, width: int, inner: int, activation: str = "silu"):
+    def __init__(self, width: int, inner: int, activation: str = "silu", gate_alpha: float = 1.0,
+                 limit: float = None, up_shift: float = 0.0):
         if activation != "silu":
             raise ValueError(f"gated_mlp supports the silu activation, got {activation!r}")
+        if limit is not None and not limit > 0:
+            raise ValueError(f"gated_mlp: the clamp limit must be positive, got {limit}")
         self.width, self.inner = int(width), int(inner)
+        self.gate_alpha, self.limit, self.up_shift = float(gate_alpha), (None if limit is None else float(limit)), float(up_shift)
+        self.plain_silu = self.gate_alpha == 1.0 and self.limit is None and self.up_shift == 0.0
         self.w_gate_up = self.w_down = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -39,5 +50,10 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, h, residual) -> None:
         act = ctx.rows("mlp.act", self.inner)
-        linear(h, self.w_gate_up, act, EPI_SWIGLU)
+        if self.plain_silu:
+            linear(h, self.w_gate_up, act, EPI_SWIGLU)
+        else:
+            pairs = ctx.rows("mlp.pairs", 2 * self.inner)
+            linear(h, self.w_gate_up, pairs, EPI_STORE)
+            ops.gate_mul(pairs, act, True, self.gate_alpha, self.limit or 0.0, self.up_shift)
         linear(act, self.w_down, residual, EPI_ACCUMULATE)

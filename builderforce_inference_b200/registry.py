@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its model.
 
-A config.json names its architecture twice: ``architectures[0]`` (a class name such as
-``Qwen3ForCausalLM``) and ``model_type`` (``qwen3``).  Either selects the entry; the lookup is
+A config.json names its architecture under ``architectures[0]`` (a class name such as
+``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``).  Any of them selects the entry; the lookup is
 exact and case-sensitive, and an unknown name is answered with the list of known ones, as in
 the reference (crates/bfi-models/src/arch.rs:70-91).
 """
@@ -45,10 +45,11 @@ def architecture_for(config: Dict[str, Any]) -> Architecture:
     archs = config.get("architectures")
     if isinstance(archs, (list, tuple)):
         candidates += [a for a in archs if isinstance(a, str)]
-    if isinstance(config.get("model_type"), str):
-        candidates.append(config["model_type"])
+    for key in ("model_type", "architecture"):
+        if isinstance(config.get(key), str):
+            candidates.append(config[key])
     if not candidates:
-        raise ConfigError("config.json names no architecture (keys 'architectures' and 'model_type'); "
+        raise ConfigError("config.json names no architecture (keys 'architectures', 'model_type', 'architecture'); "
                           f"registered: {registered_architectures()}")
     for c in candidates:
         if c in _ARCHITECTURES:
@@ -65,6 +66,10 @@ def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
     register_architecture(("qwen3", "Qwen3ForCausalLM"),
                           Architecture(name="qwen3", config_class=Qwen3Config, describe=qwen3.describe))
+    from .architectures import datasun
+    from .config.datasun import DatasunConfig
+    register_architecture(("Datasun", "datasun"),
+                          Architecture(name="datasun", config_class=DatasunConfig, describe=datasun.describe))
 
 
 _register_builtin()
