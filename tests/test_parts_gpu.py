@@ -180,7 +180,7 @@ def test_unknown_kinds_and_bad_sizes_are_refused():
     from builderforce_inference_b200.parts import MIXERS, NORMS, PartSpec
     with pytest.raises(KeyError, match="registered"):
         NORMS.build(PartSpec("layernorm", {"width": 8}))
-    with pytest.raises(ValueError, match="steps of 16"):
-        MIXERS.build(PartSpec("attention", {"width": 8, "n_heads": 2, "n_kv_heads": 1, "head_dim": 24}))
+    with pytest.raises(ValueError, match="even head sizes"):
+        MIXERS.build(PartSpec("attention", {"width": 8, "n_heads": 2, "n_kv_heads": 1, "head_dim": 23}))
     with pytest.raises(ValueError, match="GQA"):
         MIXERS.build(PartSpec("attention", {"width": 8, "n_heads": 3, "n_kv_heads": 2, "head_dim": 16}))
