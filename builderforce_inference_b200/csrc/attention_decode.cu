@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
-                        const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
+                        const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2, float sink_log2,
                         int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ status, TcWaits waits) {
     pdl_trigger();
@@ -309,6 +309,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         const int head = head0 + row;
         if (n_splits == 1) {
+            l += fast_exp2(sink_log2 - m);        // the sink's term of the denominator (none: -inf, adds 0)
             out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
             const size_t pi = ((size_t)seq * n_q + head) * max_splits + split;
@@ -329,7 +330,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 template <int D, int CAP>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
-                                              bf16* __restrict__ out, long out_stride, int n_q, int max_splits, int window) {
+                                              bf16* __restrict__ out, long out_stride, int n_q, int max_splits, int window,
+                                              float sink_log2) {
     pdl_trigger();
     const int seq = blockIdx.y, head = blockIdx.x;
     const int slot = seq_slot[seq];
@@ -361,6 +363,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
         l += ls[s] * f;
         acc = fmaf(os[s], f, acc);
     }
+    l += fast_exp2(sink_log2 - m);
     out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
 }
 
@@ -368,7 +371,7 @@ template <int D>
 static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                          const void* v_pages, long n_pages, const int* block_table, int table_stride,
                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale,
-                         int max_splits, float* part_o, float* part_ml, int* status, cudaStream_t stream, TcWaits waits) {
+                         float sink, int max_splits, float* part_o, float* part_ml, int* status, cudaStream_t stream, TcWaits waits) {
     CUtensorMap mk, mv;
     int rc = bfi_tensor_map_bf16(k_pages, n_pages * n_kv * AD_TILE, D, D, AD_TILE, &mk);
     if (rc) return rc;
@@ -385,14 +388,15 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     }
     dim3 grid(max_splits, n_kv * head_chunks, n_seqs);
     const float scale_log2 = scale * 1.4426950408889634f;
+    const float sink_log2 = sink * 1.4426950408889634f;       // -inf: no sink
     bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
-               block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml,
+               block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window, scale_log2, sink_log2, head_chunks, part_o, part_ml,
                status, waits);
     rc = bfi_check_launch("attention_decode");
     if (rc || max_splits == 1) return rc;
 #define BFI_MERGE(CAP)                                                                                                   \
     bfi_launch(attention_decode_merge_kernel<D, CAP>, dim3(n_q, n_seqs), dim3(D), 0, stream, (const float*)part_o,        \
-               (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits, window)
+               (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits, window, sink_log2)
     if (max_splits <= 8) BFI_MERGE(8);
     else if (max_splits <= 16) BFI_MERGE(16);
     else BFI_MERGE(32);
@@ -405,11 +409,12 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
 // Every sequence's pages are cut into at most `max_splits` (up to 32) ranges.  With max_splits > 1 the caller
 // gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.  `status` points at
 // an int, zero before the first call, that gets BFI_STATUS_TIMEOUT when a wait for a page ran out.
+// `sink`: a score beside the keys' whose exponential joins the softmax's denominator; -infinity for none.
 static int attention_decode_launch(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                    const void* v_pages, long n_pages, const int* block_table, int table_stride,
                                    const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv, int d,
-                                   int window, float scale, int max_splits, float* part_o, float* part_ml, int* status,
-                                   cudaStream_t stream, TcWaits waits) {
+                                   int window, float scale, float sink, int max_splits, float* part_o, float* part_ml,
+                                   int* status, cudaStream_t stream, TcWaits waits) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 32, "attention_decode: bad window or split count (1..32)");
@@ -421,20 +426,20 @@ static int attention_decode_launch(const void* q, long q_stride, void* out, long
     if (max_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
     if (d == 64)
         return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
-                                 seq_slot, seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status,
+                                 seq_slot, seq_start, n_seqs, n_q, n_kv, window, scale, sink, max_splits, part_o, part_ml, status,
                                  stream, waits);
     return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride, seq_slot,
-                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status, stream,
+                              seq_start, n_seqs, n_q, n_kv, window, scale, sink, max_splits, part_o, part_ml, status, stream,
                               waits);
 }
 
 extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                          const void* v_pages, long n_pages, const int* block_table, int table_stride,
                                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
-                                         int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
-                                         int* status, cudaStream_t stream) {
+                                         int d, int window, float scale, float sink, int max_splits, float* part_o,
+                                         float* part_ml, int* status, cudaStream_t stream) {
     return attention_decode_launch(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
-                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, max_splits, part_o, part_ml,
+                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, sink, max_splits, part_o, part_ml,
                                    status, stream, tc_waits_default());
 }
 
@@ -451,7 +456,7 @@ extern "C" int bfi_attention_decode_bf16_wait_probe(const void* q, long q_stride
                                                     cudaStream_t stream) {
     BFI_REQUIRE(spin_limit > 0 && spin_limit <= TC_SPIN_LIMIT, "attention_decode probe: spin limit out of range");
     return attention_decode_launch(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
-                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, max_splits, part_o, part_ml,
+                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, -INFINITY, max_splits, part_o, part_ml,
                                    status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
 }
 

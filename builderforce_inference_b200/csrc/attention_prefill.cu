@@ -19,7 +19,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv,
-                         int window, float scale_log2) {
+                         int window, float scale_log2, float sink_log2) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -205,7 +205,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
     for (int r = 0; r < 2; ++r) {
         const int tok = tok0 + warp * 16 + g + r * 8;
         if (tok >= nt) continue;
-        const float inv = l_run[r] > 0.0f ? 1.0f / l_run[r] : 0.0f;
+        // the sink's term of the denominator (no sink: -inf, which adds 0)
+        const float l_all = l_run[r] + (m_run[r] == -INFINITY ? 0.0f : fast_exp2(sink_log2 - m_run[r]));
+        const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
         bf16* orow = out + (size_t)(t0 + tok) * out_stride + (size_t)head * D;
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
@@ -219,7 +221,7 @@ template <int D>
 static int launch_prefill(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                           const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                           const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv,
-                          int window, float scale, cudaStream_t stream) {
+                          int window, float scale, float sink, cudaStream_t stream) {
     const size_t smem = (size_t)(AP_QROWS * D + 4 * AD_TILE * D) * sizeof(bf16);
     auto kernel = attention_prefill_kernel<D>;
     if (smem > 48 * 1024) {
@@ -230,15 +232,16 @@ static int launch_prefill(const void* q, long q_stride, void* out, long out_stri
     dim3 grid((max_tokens + AP_QROWS - 1) / AP_QROWS, n_q, n_seqs);
     bfi_launch(kernel, grid, dim3(AD_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, cu_seqlens, seq_slot, seq_start, n_q,
-               n_kv, window, scale * 1.4426950408889634f);
+               n_kv, window, scale * 1.4426950408889634f, sink * 1.4426950408889634f);
     return bfi_check_launch("attention_prefill");
 }
 
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+// `sink`: a score beside the keys' whose exponential joins the softmax's denominator; -infinity for none.
 extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                           const void* v_pages, const int* block_table, int table_stride,
                                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
-                                          int max_tokens, int n_q, int n_kv, int d, int window, float scale,
+                                          int max_tokens, int n_q, int n_kv, int d, int window, float scale, float sink,
                                           cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
@@ -250,7 +253,7 @@ extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* ou
         return 2;
     if (d == 64)
         return launch_prefill<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, stream);
+                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, sink, stream);
     return launch_prefill<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, stream);
+                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, sink, stream);
 }

@@ -175,7 +175,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_seqs, int max_tiles,
-                            int n_q, int n_kv, int window, float scale_log2, uint32_t v_lbo, uint32_t v_sbo,
+                            int n_q, int n_kv, int window, float scale_log2, float sink_log2, uint32_t v_lbo, uint32_t v_sbo,
                             int* __restrict__ status, int* __restrict__ counters, TcWaits waits) {
     const uint32_t spin_limit = waits.spin_limit;
     constexpr int BOXES = D / 64;
@@ -591,7 +591,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             if (!ok) break;
             pending = true;
-            e_it = it, e_row0 = row0, e_rows = rows, e_head = head, e_l = l_run;
+            e_it = it, e_row0 = row0, e_rows = rows, e_head = head;
+            // the sink's term of the denominator, in the units of the row's shift (no sink: -inf, which adds 0)
+            e_l = l_run + (m_used == -INFINITY ? 0.0f : ft_exp2(sink_log2 - m_used * scale_log2));
         }
         if (ok && pending && !write_out()) timed_out = true;
         if (timed_out && lane == 0) {
@@ -632,7 +634,7 @@ template <int D>
 static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out_stride, const void* k_pages,
                              const void* v_pages, long n_pages, const int* block_table, int table_stride,
                              const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs, long n_tokens,
-                             int max_seq_tokens, int n_q, int n_kv, int window, float scale, int* status,
+                             int max_seq_tokens, int n_q, int n_kv, int window, float scale, float sink, int* status,
                              cudaStream_t stream, TcWaits waits) {
     CUtensorMap mq, mk, mv;
     int rc = bfi_tensor_map_bf16(qkv, n_tokens, (long)n_q * D, q_stride, FT_ROWS, &mq);
@@ -661,7 +663,7 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
     dim3 grid((unsigned)(items < n_sm ? items : n_sm));      // one block per SM, each drawing items until none is left
     bfi_launch(kernel, grid, dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, out_stride, block_table, table_stride,
                cu_seqlens, seq_slot, seq_start, n_seqs, max_tiles, n_q, n_kv, window, scale * 1.4426950408889634f,
-               (uint32_t)lbo, (uint32_t)sbo, status, status + 1, waits);
+               sink * 1.4426950408889634f, (uint32_t)lbo, (uint32_t)sbo, status, status + 1, waits);
     return bfi_check_launch("attention_prefill_tcgen05");
 }
 
@@ -671,12 +673,13 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
 // head sizes other than 64/128, or operands TMA cannot address.  `status` points at three ints,
 // zero before the first call: [0] gets BFI_STATUS_TIMEOUT when a wait ran out, [1] and [2] are
 // the counters of tickets drawn and blocks finished, which every launch leaves at zero again; two
-// launches that may run at the same time need status words of their own.
+// launches that may run at the same time need status words of their own.  `sink`: a score beside the
+// keys' whose exponential joins the softmax's denominator; -infinity for none.
 static int attention_prefill_tc_launch(const void* qkv, long q_stride, void* out, long out_stride, const void* k_pages,
                                        const void* v_pages, long n_pages, const int* block_table, int table_stride,
                                        const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
                                        long n_tokens, int max_seq_tokens, int n_q, int n_kv, int d, int window, float scale,
-                                       int* status, cudaStream_t stream, TcWaits waits) {
+                                       float sink, int* status, cudaStream_t stream, TcWaits waits) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tcgen05: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && status != nullptr, "attention_prefill_tcgen05: bad window or no status word");
@@ -689,10 +692,10 @@ static int attention_prefill_tc_launch(const void* qkv, long q_stride, void* out
     if (d == 64)
         return launch_prefill_tc<64>(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                      cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, window,
-                                     scale, status, stream, waits);
+                                     scale, sink, status, stream, waits);
     return launch_prefill_tc<128>(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                   cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, window, scale,
-                                  status, stream, waits);
+                                  sink, status, stream, waits);
 }
 
 extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride, void* out, long out_stride,
@@ -700,10 +703,10 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride
                                                   const int* block_table, int table_stride, const int* cu_seqlens,
                                                   const int* seq_slot, const int* seq_start, int n_seqs, long n_tokens,
                                                   int max_seq_tokens, int n_q, int n_kv, int d, int window, float scale,
-                                                  int* status, cudaStream_t stream) {
+                                                  float sink, int* status, cudaStream_t stream) {
     return attention_prefill_tc_launch(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                        cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, d, window,
-                                       scale, status, stream, tc_waits_default());
+                                       scale, sink, status, stream, tc_waits_default());
 }
 
 // For the tests of the time-out path: the same launch, but every bounded wait gives up after
@@ -723,7 +726,7 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16_wait_probe(const void* qkv, lo
                 spin_limit);
     return attention_prefill_tc_launch(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                        cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, d, window,
-                                       scale, status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
+                                       scale, -INFINITY, status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
 }
 
 BFI_TRACE_EXPORT(attention_prefill_tcgen05)

@@ -1,0 +1,268 @@
+// Linear attention with a per-head decay over runs of new tokens, on the tensor cores: the same
+// recurrence as lightning.cu (S_t = w S_(t-1) + k_t v_t^T, o_t = S_t^T q_t), evaluated a chunk of
+// 64 tokens at a time.  With S the state before the chunk, t and j counted inside the chunk and n
+// its length:
+//     o_t  = w^(t+1) (q_t S)  +  sum_{j <= t} w^(t-j) (q_t . k_j) v_j
+//     S'   = w^n S  +  sum_j w^(n-1-j) k_j v_j^T
+// Only non-negative powers of w appear, so any decay in [0, 1] is safe.  q, k, v are the activated
+// projections rounded to bfloat16 (products of two bfloat16 values are exact in float32); the
+// state, the scores, the decayed weights and every sum are float32.  Where a float32 matrix has
+// to be a tensor-core operand (S in q S, the decayed scores, the decayed values) it is split
+// into a bfloat16 head and a bfloat16 remainder and the product is taken with both, which keeps
+// 16 bits of mantissa; the master copy of the state stays float32 and is only ever added to.
+//
+// A block owns VB columns of one head of one sequence and walks the sequence's chunks in order;
+// the matrix products are 16x16x16 tiles dealt round-robin to its 8 warps.
+#include <mma.h>
+
+#include "common.cuh"
+
+using namespace nvcuda;
+
+#define LC 64          // tokens per chunk
+#define LC_WARPS 8
+
+__device__ __forceinline__ float lc_silu(float x) { return x / (1.0f + __expf(-x)); }
+
+struct LcSmem {
+    int ldq, ldv, lda, ldaf, ldof, ldsf;
+    size_t q, k, v, af, ahi, alo, of, vhi, vlo, sf, shi, slo, pw, total;
+};
+
+static __host__ __device__ inline LcSmem lc_layout(int D, int VB) {
+    LcSmem s;
+    s.ldq = D + 8, s.ldv = VB + 8, s.lda = LC + 8, s.ldaf = LC + 4, s.ldof = VB + 4, s.ldsf = VB + 4;
+    size_t o = 0;
+    auto take = [&](size_t bytes) { size_t at = o; o += (bytes + 127) / 128 * 128; return at; };
+    s.q = take((size_t)LC * s.ldq * 2);
+    s.k = take((size_t)LC * s.ldq * 2);
+    s.v = take((size_t)LC * s.ldv * 2);
+    s.af = take((size_t)LC * s.ldaf * 4);
+    s.ahi = take((size_t)LC * s.lda * 2);
+    s.alo = take((size_t)LC * s.lda * 2);
+    s.of = take((size_t)LC * s.ldof * 4);
+    s.vhi = take((size_t)LC * s.ldv * 2);
+    s.vlo = take((size_t)LC * s.ldv * 2);
+    s.sf = take((size_t)D * s.ldsf * 4);
+    s.shi = take((size_t)D * s.ldv * 2);
+    s.slo = take((size_t)D * s.ldv * 2);
+    s.pw = take((size_t)(LC + 1) * 4);
+    s.total = o;
+    return s;
+}
+
+__device__ __forceinline__ void lc_split(float x, bf16& hi, bf16& lo) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+
+template <int VB>
+__global__ void __launch_bounds__(LC_WARPS * 32)
+lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
+                       long out_stride, float* __restrict__ state, const float* __restrict__ decay,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int H, int D, int V,
+                       int v_blocks) {
+    pdl_trigger();
+    extern __shared__ __align__(128) unsigned char lc_smem[];
+    const LcSmem L = lc_layout(D, VB);
+    bf16* Qs = reinterpret_cast<bf16*>(lc_smem + L.q);
+    bf16* Ks = reinterpret_cast<bf16*>(lc_smem + L.k);
+    bf16* Vs = reinterpret_cast<bf16*>(lc_smem + L.v);
+    float* Af = reinterpret_cast<float*>(lc_smem + L.af);
+    bf16* Ahi = reinterpret_cast<bf16*>(lc_smem + L.ahi);
+    bf16* Alo = reinterpret_cast<bf16*>(lc_smem + L.alo);
+    float* Of = reinterpret_cast<float*>(lc_smem + L.of);
+    bf16* Vhi = reinterpret_cast<bf16*>(lc_smem + L.vhi);
+    bf16* Vlo = reinterpret_cast<bf16*>(lc_smem + L.vlo);
+    float* Sf = reinterpret_cast<float*>(lc_smem + L.sf);
+    bf16* Shi = reinterpret_cast<bf16*>(lc_smem + L.shi);
+    bf16* Slo = reinterpret_cast<bf16*>(lc_smem + L.slo);
+    float* pw = reinterpret_cast<float*>(lc_smem + L.pw);
+
+    const int seq = blockIdx.y;
+    const int slot = seq_slot[seq];
+    if (slot < 0) return;
+    const int h = blockIdx.x / v_blocks;
+    const int v0 = (blockIdx.x - h * v_blocks) * VB;
+    const int t0 = cu_seqlens[seq], nt = cu_seqlens[seq + 1] - t0;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int DT = D / 16, VT = VB / 16, CT = LC / 16;
+    const float w = decay[h];
+    for (int p = tid; p <= LC; p += blockDim.x) pw[p] = powf(w, (float)p);
+    // the state earlier steps left (zero for a fresh slot): not written by this step's kernels
+    float* sp = state + (((size_t)slot * H + h) * D) * V + v0;
+    for (int i = tid; i < D * VB; i += blockDim.x) {
+        const int d = i / VB, c = i - d * VB;
+        const float s = v0 + c < V ? sp[(size_t)d * V + c] : 0.0f;
+        Sf[d * L.ldsf + c] = s;
+        lc_split(s, Shi[d * L.ldv + c], Slo[d * L.ldv + c]);
+    }
+    pdl_wait();
+
+    for (int c0 = 0; c0 < nt; c0 += LC) {
+        const int n = min(LC, nt - c0);
+        // ---- the chunk's q, k (all of the head) and v (this block's columns), activated, as bfloat16
+        for (int i = tid; i < LC * (D / 2); i += blockDim.x) {
+            const int t = i / (D / 2), e = (i - t * (D / 2)) * 2;
+            __nv_bfloat162 qv = __floats2bfloat162_rn(0.0f, 0.0f), kv = qv;
+            if (t < n) {
+                const bf16* row = proj + (size_t)(t0 + c0 + t) * stride + (size_t)h * D + e;
+                const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(row + q_off);
+                const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(row + k_off);
+                qv = __floats2bfloat162_rn(lc_silu(__low2float(q2)), lc_silu(__high2float(q2)));
+                kv = __floats2bfloat162_rn(lc_silu(__low2float(k2)), lc_silu(__high2float(k2)));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(Qs + t * L.ldq + e) = qv;
+            *reinterpret_cast<__nv_bfloat162*>(Ks + t * L.ldq + e) = kv;
+        }
+        for (int i = tid; i < LC * VB; i += blockDim.x) {
+            const int t = i / VB, c = i - t * VB;
+            float x = 0.0f;
+            if (t < n && v0 + c < V)
+                x = lc_silu(__bfloat162float(proj[(size_t)(t0 + c0 + t) * stride + v_off + (size_t)h * V + v0 + c]));
+            Vs[t * L.ldv + c] = __float2bfloat16_rn(x);
+        }
+        __syncthreads();
+
+        // ---- scores q k^T (tiles at or below the diagonal) and q S
+        const int n_a = CT * (CT + 1) / 2, n_o = CT * VT;
+        for (int job = warp; job < n_a + n_o; job += LC_WARPS) {
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+            wmma::fill_fragment(acc, 0.0f);
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+            if (job < n_a) {
+                int ti = 0, rest = job;
+                while (rest > ti) rest -= ++ti;              // job -> (ti, tj) with tj <= ti
+                const int tj = rest;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
+                for (int kk = 0; kk < DT; ++kk) {
+                    wmma::load_matrix_sync(a, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
+                    wmma::load_matrix_sync(b, Ks + tj * 16 * L.ldq + kk * 16, L.ldq);
+                    wmma::mma_sync(acc, a, b, acc);
+                }
+                wmma::store_matrix_sync(Af + ti * 16 * L.ldaf + tj * 16, acc, L.ldaf, wmma::mem_row_major);
+            } else {
+                const int ti = (job - n_a) / VT, tv = (job - n_a) - ti * VT;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+                for (int kk = 0; kk < DT; ++kk) {
+                    wmma::load_matrix_sync(a, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
+                    wmma::load_matrix_sync(b, Shi + kk * 16 * L.ldv + tv * 16, L.ldv);
+                    wmma::mma_sync(acc, a, b, acc);
+                    wmma::load_matrix_sync(b, Slo + kk * 16 * L.ldv + tv * 16, L.ldv);
+                    wmma::mma_sync(acc, a, b, acc);
+                }
+                wmma::store_matrix_sync(Of + ti * 16 * L.ldof + tv * 16, acc, L.ldof, wmma::mem_row_major);
+            }
+        }
+        __syncthreads();
+
+        // ---- the decays, in float32: scores, the q S rows, the values for the state, the state itself
+        for (int i = tid; i < LC * LC; i += blockDim.x) {
+            const int t = i / LC, j = i - t * LC;
+            const float x = j <= t ? pw[t - j] * Af[t * L.ldaf + j] : 0.0f;
+            lc_split(x, Ahi[t * L.lda + j], Alo[t * L.lda + j]);
+        }
+        for (int i = tid; i < LC * VB; i += blockDim.x) {
+            const int t = i / VB, c = i - t * VB;
+            Of[t * L.ldof + c] *= pw[t + 1];
+            const float x = t < n ? pw[n - 1 - t] * __bfloat162float(Vs[t * L.ldv + c]) : 0.0f;
+            lc_split(x, Vhi[t * L.ldv + c], Vlo[t * L.ldv + c]);
+        }
+        for (int i = tid; i < D * VB; i += blockDim.x) {
+            const int d = i / VB, c = i - d * VB;
+            Sf[d * L.ldsf + c] *= pw[n];
+        }
+        __syncthreads();
+
+        // ---- o += (decayed scores) v ;  S += k^T (decayed v)
+        const int n_s = DT * VT;
+        for (int job = warp; job < n_o + n_s; job += LC_WARPS) {
+            wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+            if (job < n_o) {
+                const int ti = job / VT, tv = job - ti * VT;
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                wmma::load_matrix_sync(acc, Of + ti * 16 * L.ldof + tv * 16, L.ldof, wmma::mem_row_major);
+                for (int kj = 0; kj <= ti; ++kj) {
+                    wmma::load_matrix_sync(b, Vs + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    wmma::load_matrix_sync(a, Ahi + ti * 16 * L.lda + kj * 16, L.lda);
+                    wmma::mma_sync(acc, a, b, acc);
+                    wmma::load_matrix_sync(a, Alo + ti * 16 * L.lda + kj * 16, L.lda);
+                    wmma::mma_sync(acc, a, b, acc);
+                }
+                wmma::store_matrix_sync(Of + ti * 16 * L.ldof + tv * 16, acc, L.ldof, wmma::mem_row_major);
+            } else {
+                const int td = (job - n_o) / VT, tv = (job - n_o) - td * VT;
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::col_major> a;      // k^T: [d][j] = Ks[j][d]
+                wmma::load_matrix_sync(acc, Sf + td * 16 * L.ldsf + tv * 16, L.ldsf, wmma::mem_row_major);
+                for (int kj = 0; kj < CT; ++kj) {
+                    wmma::load_matrix_sync(a, Ks + kj * 16 * L.ldq + td * 16, L.ldq);
+                    wmma::load_matrix_sync(b, Vhi + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    wmma::mma_sync(acc, a, b, acc);
+                    wmma::load_matrix_sync(b, Vlo + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    wmma::mma_sync(acc, a, b, acc);
+                }
+                wmma::store_matrix_sync(Sf + td * 16 * L.ldsf + tv * 16, acc, L.ldsf, wmma::mem_row_major);
+            }
+        }
+        __syncthreads();
+
+        // ---- the chunk's outputs, and the new state split for the next chunk
+        for (int i = tid; i < n * VB; i += blockDim.x) {
+            const int t = i / VB, c = i - t * VB;
+            if (v0 + c < V) out[(size_t)(t0 + c0 + t) * out_stride + (size_t)h * V + v0 + c] = Of[t * L.ldof + c];
+        }
+        for (int i = tid; i < D * VB; i += blockDim.x) {
+            const int d = i / VB, c = i - d * VB;
+            lc_split(Sf[d * L.ldsf + c], Shi[d * L.ldv + c], Slo[d * L.ldv + c]);
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < D * VB; i += blockDim.x) {
+        const int d = i / VB, c = i - d * VB;
+        if (v0 + c < V) sp[(size_t)d * V + c] = Sf[d * L.ldsf + c];
+    }
+}
+
+template <int VB>
+static int launch_chunks(const bf16* proj, long stride, int q_off, int k_off, int v_off, float* out, long out_stride,
+                         float* state, const float* decay, const int* cu_seqlens, const int* seq_slot, int n_seqs, int H,
+                         int D, int V, cudaStream_t stream) {
+    const LcSmem L = lc_layout(D, VB);
+    const int v_blocks = (V + VB - 1) / VB;
+    auto kernel = lightning_chunk_kernel<VB>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
+    if (e != cudaSuccess) return bfi_fail("lightning_chunks: cannot reserve %zu bytes of shared memory: %s", L.total, cudaGetErrorString(e));
+    bfi_launch(kernel, dim3(H * v_blocks, n_seqs), dim3(LC_WARPS * 32), L.total, stream, proj, stride, q_off, k_off, v_off, out,
+               out_stride, state, decay, cu_seqlens, seq_slot, H, D, V, v_blocks);
+    return bfi_check_launch("lightning_chunks");
+}
+
+// Returns 2 ("not taken") for sizes this kernel does not handle; the caller then runs the general one.
+extern "C" int bfi_lightning_chunks_bf16(const void* proj, long stride, int q_off, int k_off, int v_off, float* out,
+                                         long out_stride, float* state, const float* decay, const int* cu_seqlens,
+                                         const int* seq_slot, int n_seqs, int H, int D, int V, cudaStream_t stream) {
+    BFI_REQUIRE(H > 0 && D > 0 && V > 0, "lightning_chunks: bad sizes heads=%d dim=%d vdim=%d", H, D, V);
+    BFI_REQUIRE(out_stride >= (long)H * V, "lightning_chunks: output stride shorter than the heads");
+    if (n_seqs <= 0) return 0;
+    if (D % 16 != 0 || V % 16 != 0 || n_seqs > 65535) return 2;
+    // q and k are read as pairs: their columns must start on 4-byte boundaries
+    if (((uintptr_t)proj & 3) != 0 || stride % 2 != 0 || q_off % 2 != 0 || k_off % 2 != 0) return 2;
+    // columns per block: as many as fit shared memory, fewer when that is needed to fill the GPU
+    const size_t limit = 200 * 1024;
+    int vb = 0;
+    for (int cand : {64, 32, 16}) {
+        if (V % cand != 0 && cand != 16) continue;
+        if (lc_layout(D, cand).total > limit) continue;
+        if (vb == 0) vb = cand;
+        if ((long)n_seqs * H * ((V + vb - 1) / vb) >= bfi_sm_count()) break;
+        vb = cand;
+    }
+    if (vb == 0) return 2;
+    const bf16* p = (const bf16*)proj;
+    if (vb == 64) return launch_chunks<64>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
+    if (vb == 32) return launch_chunks<32>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
+    return launch_chunks<16>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
+}
+
+BFI_TRACE_EXPORT(lightning_chunked)

@@ -182,8 +182,13 @@ def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int, n_sm: int)
     return max(1, min(max(fill, length), max_pages, 32))
 
 
+def _sink(sink) -> c_float:
+    """A sink's score for the kernels: minus infinity stands for none."""
+    return c_float(float("-inf") if sink is None else float(sink))
+
+
 def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
-                          probe=None) -> bool:
+                          probe=None, sink=None) -> bool:
     """One new token per sequence over its cached pages, which arrive by TMA: the cache must be
     contiguous.  A wait for a page that ran out shows in ``tc_status``.  ``probe``: (polls, hold
     the producer), for ``attention_decode_wait_probe``."""
@@ -207,9 +212,11 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
     args = [_ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v),
             c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot),
             _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0),
-            c_float(scale), c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(tc_status(qkv.device))]
+            c_float(scale)]
+    tail = [c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(tc_status(qkv.device))]
     if probe is None:
-        return library("fast").call_optional("bfi_attention_decode_bf16", *args, _stream())
+        return library("fast").call_optional("bfi_attention_decode_bf16", *args, _sink(sink), *tail, _stream())
+    args += tail
     return library("fast").call_optional("bfi_attention_decode_bf16_wait_probe", *args, c_int(int(probe[0])),
                                          c_int(1 if probe[1] else 0), _stream())
 
@@ -221,7 +228,7 @@ def attention_decode_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n
     return attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale, probe=(spin_limit, hold_producer))
 
 
-def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sink=None) -> bool:
     """Tensor-core attention for steps that bring more than one token per sequence."""
     d = kv.head_dim
     if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
@@ -230,13 +237,14 @@ def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_head
         "bfi_attention_prefill_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot),
         _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads),
-        c_int(d), c_int(kv.window or 0), c_float(scale), _stream())
+        c_int(d), c_int(kv.window or 0), c_float(scale), _sink(sink), _stream())
 
 
 TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles
 
 
-def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
+                                   sink=None) -> bool:
     """tcgen05 / TMA attention for steps with long runs of new tokens: one block per SM draws
     items of 128 tokens of one head, scores and output in tensor memory.  A wait that ran out
     shows in ``tc_status``."""
@@ -250,7 +258,7 @@ def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv
         _ptr(kv.k), _ptr(kv.v), c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)),
         _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_long(qkv.shape[0]),
         c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
-        _ptr(tc_status(qkv.device)), _stream())
+        _sink(sink), _ptr(tc_status(qkv.device)), _stream())
 
 
 def attention_prefill_tcgen05_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
@@ -264,3 +272,24 @@ def attention_prefill_tcgen05_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tens
         c_long(qkv.shape[0]), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim),
         c_int(kv.window or 0), c_float(scale), _ptr(tc_status(qkv.device)), c_int(int(spin_limit)),
         c_int(1 if hold_producer else 0), _stream())
+
+
+LIGHTNING_CHUNK_MIN_TOKENS = 8     # shorter runs of new tokens: the token-by-token kernel
+
+
+def lightning_chunks_bf16(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
+                          decay: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+                          n_heads: int, dim: int, vdim: int) -> bool:
+    """The decayed linear attention over runs of new tokens, 64 at a time on the tensor cores (SiLU
+    on q, k, v applied as they are read).  Same arguments and state as ``ops.lightning_scan``;
+    False for sizes it does not take (head sizes that are no multiples of 16, or too large)."""
+    if proj.dtype != torch.bfloat16 or out.dtype != torch.float32 or state.dtype != torch.float32:
+        return False
+    _rows_2d(proj, "projections")
+    _rows_2d(out, "recurrence output")
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim) or out.shape[1] != n_heads * vdim:
+        raise KernelError("lightning_chunks: state [slots, heads, dim, vdim] and output [tokens, heads * vdim] expected")
+    return library("fast").call_optional(
+        "bfi_lightning_chunks_bf16", _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off),
+        _ptr(out), c_long(out.stride(0)), _ptr(state), _ptr(decay), _ptr(cu_seqlens), _ptr(seq_slot), c_int(n_seqs),
+        c_int(n_heads), c_int(dim), c_int(vdim), _stream())

@@ -70,5 +70,11 @@ class LightningAttention(Mixer):
 
     def recur(self, ctx, proj, o, state) -> None:
         qk = self.n_heads * self.dim
+        if proj.dtype == torch.bfloat16:
+            from ..kernels import fast_ops
+            if ctx.max_seq_tokens >= fast_ops.LIGHTNING_CHUNK_MIN_TOKENS and fast_ops.lightning_chunks_bf16(
+                    proj, 0, qk, 2 * qk, o, state, self.decay, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
+                    self.n_heads, self.dim, self.vdim):
+                return
         ops.lightning_scan(proj, 0, qk, 2 * qk, o, state, self.decay, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
                            self.n_heads, self.dim, self.vdim, ops.LIGHT_ACT_SILU, few_tokens=ctx.max_seq_tokens == 1)

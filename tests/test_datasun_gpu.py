@@ -378,6 +378,109 @@ def test_lightning_kernel_whole_in_portions_and_token_by_token(dt, H, D, V):
     assert rel_err(state[3].double().cpu(), refs[0][1]) < t
 
 
+def test_lightning_chunked_kernel_against_the_plain_recurrence_on_the_same_bfloat16_values():
+    """The tensor-core kernel rounds the activated q, k, v to bfloat16 and nothing else: against
+    the plain recurrence on those rounded values it is exact to float32-like accuracy, whatever the
+    decay; whole, in portions that end inside a chunk, and mixed with short sequences."""
+    from builderforce_inference_b200.kernels import fast_ops
+    for H, D, V, decay in ((2, 64, 64, [0.999, 0.6]), (3, 32, 128, [1.0, 0.93, 0.05]), (1, 128, 48, [0.97]), (2, 16, 16, [0.9, 0.5])):
+        g = torch.Generator().manual_seed(H + D + V)
+        lens, slots = [200, 9, 70], [3, 0, 2]
+        dec = torch.tensor(decay, dtype=F32, device=DEV)
+        cols = 2 * H * D + 2 * H * V
+        projs = [torch.randn(n, cols, generator=g).to(BF16) for n in lens]
+        projs[0][5] *= 6.0
+        refs = []
+        for p in projs:
+            x = P.silu(p.double()).to(BF16).double()
+            n = p.shape[0]
+            o, S = P.lightning_recurrence(x[:, :H * D].reshape(n, H, D), x[:, H * D:2 * H * D].reshape(n, H, D),
+                                          x[:, 2 * H * D:2 * H * D + H * V].reshape(n, H, V), decay)
+            refs.append((o.reshape(n, H * V), S))
+
+        def run(proj, state, seqs):
+            cu = [0]
+            for _, n in seqs:
+                cu.append(cu[-1] + n)
+            o = torch.full((cu[-1], H * V), float("nan"), dtype=F32, device=DEV)
+            assert fast_ops.lightning_chunks_bf16(proj.to(DEV), 0, H * D, 2 * H * D, o, state, dec, i32(cu),
+                                                  i32([s for s, _ in seqs]), len(seqs), H, D, V)
+            return o.double().cpu()
+
+        state = torch.zeros(4, H, D, V, dtype=F32, device=DEV)
+        got = run(torch.cat(projs), state, list(zip(slots, lens)))
+        at = 0
+        for (o, S), n, sl in zip(refs, lens, slots):
+            assert rel_err(got[at:at + n], o) < 3e-3, (H, D, V)
+            assert rel_err(state[sl].double().cpu(), S) < 3e-3
+            at += n
+        state.zero_()
+        outs, at = [], 0
+        for c in (64, 2, 70, 63, 1):
+            outs.append(run(projs[0][at:at + c], state, [(3, c)]))
+            at += c
+        assert at == lens[0] and rel_err(torch.cat(outs), refs[0][0]) < 3e-3
+        # and the two kernels agree on a state they hand to one another
+        mid = scan(projs[0][:100].to(DEV), state.zero_(), dec, [(3, 100)], H, D, V)
+        rest = run(projs[0][100:], state, [(3, 100)])
+        assert rel_err(torch.cat([mid, rest]), refs[0][0]) < 3e-3
+    assert not fast_ops.lightning_chunks_bf16(torch.zeros(4, 2 * 24 + 2 * 20, dtype=BF16, device=DEV), 0, 24, 48,
+                                              torch.zeros(4, 20, device=DEV), torch.zeros(1, 1, 24, 20, device=DEV),
+                                              torch.ones(1, device=DEV), i32([0, 4]), i32([0]), 1, 1, 24, 20)
+
+
+class StepShape:
+    """The fields of a step context the bfloat16 attention kernels read."""
+
+    def __init__(self, seqs):
+        from builderforce_inference_b200.engine.context import Workspace
+        cu = [0]
+        for _, _, t in seqs:
+            cu.append(cu[-1] + t)
+        self.n_seqs, self.n_tokens = len(seqs), cu[-1]
+        self.max_seq_tokens = max(t for _, _, t in seqs)
+        self.cu_seqlens, self.seq_slot, self.seq_start = i32(cu), i32([s for s, _, _ in seqs]), i32([st for _, st, _ in seqs])
+        self.workspace = Workspace(DEV)
+
+
+@pytest.mark.parametrize("kernel", ["decode", "mma", "tcgen05"])
+@pytest.mark.parametrize("n_q,n_kv,d,window,sink", [(8, 2, 64, 100, 0.0), (6, 1, 64, 40, 0.0), (4, 4, 128, None, 2.0), (2, 1, 128, 70, -1.0)])
+def test_sink_in_the_bfloat16_attention_kernels(kernel, n_q, n_kv, d, window, sink, monkeypatch):
+    from builderforce_inference_b200.kernels import fast_ops
+    g = torch.Generator().manual_seed(n_q + d)
+    if kernel == "decode":
+        seqs = [(0, 0, 1), (1, 63, 1), (2, 64, 1), (3, 300, 1), (4, 39, 1), (5, 40, 1)]
+    else:
+        seqs = [(2, 0, 33), (0, 0, 1), (1, 31, 34), (4, 64, 64), (5, 0, 200), (3, 63, 130)]
+    pages = Pages(6, 400, n_kv, d, BF16, window, seed=d)
+    qs, refs = [], []
+    for slot, start, t in seqs:
+        k = torch.randn(start + t, n_kv, d, generator=g)
+        v = torch.randn(start + t, n_kv, d, generator=g)
+        q = torch.randn(t, n_q, d, generator=g)
+        pages.write(slot, 0, k, v)
+        kk, vv = pages.read(slot, start + t)
+        refs.append(P.sink_attention(q64(q, BF16), kk, vv, 0.17, window, sink, start).reshape(t, n_q * d))
+        qs.append(q.reshape(t, n_q * d))
+    q_all = torch.cat(qs).to(BF16).to(DEV)
+    ref = torch.cat(refs)
+    fn = {"decode": fast_ops.attention_decode_bf16, "mma": fast_ops.attention_prefill_bf16,
+          "tcgen05": fast_ops.attention_prefill_tcgen05_bf16}[kernel]
+    for forced in ((None, 1, 3) if kernel == "decode" else (None,)):      # one page range per sequence, and several merged
+        if forced is not None:
+            monkeypatch.setattr(fast_ops, "decode_splits", lambda *a, f=forced: f)
+        out = torch.full(q_all.shape, float("nan"), dtype=BF16, device=DEV)
+        assert fn(StepShape(seqs), q_all, out, pages.view, n_q, 0.17, sink=sink)
+        assert rel_err(out.double().cpu(), ref) < 1e-2, forced
+        # the same launch without the sink differs: the test would see a sink that is left out
+        out2 = torch.full(q_all.shape, float("nan"), dtype=BF16, device=DEV)
+        assert fn(StepShape(seqs), q_all, out2, pages.view, n_q, 0.17)
+        assert rel_err(out2.double().cpu(), ref) > 3e-2
+    st = fast_ops.tc_status(DEV)
+    assert int(st[0]) == 0
+    st.zero_()
+
+
 @pytest.mark.parametrize("dt", [F32, BF16])
 def test_gate_mul_clamps_and_shifts(dt):
     g = torch.Generator().manual_seed(0)
