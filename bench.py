@@ -17,6 +17,11 @@ has the layer sizes of the benchmark configuration with random weights and synth
 batch of 16 prompts of 64 to 4,096 tokens with 256 decode steps and an 8,192-token prompt; decode
 at batch 1 and 32 behind 2,048-token prompts and a 2,048-token prompt) and print one line each.
 
+``--design datasun`` leaves the benchmark aside and runs the Datasun design (parallel blocks,
+three lightning-attention layers to one windowed softmax-attention layer) beside Qwen3 at equal
+layer sizes, a few sizes, random weights: a 2,048-token prompt with its breakdown by kernel class,
+and decode at batch 8 and 64 behind 1,024-token prompts.  One line.
+
 The work is one GPU's: for ``--gpus`` above 1 it says so and exits with 2.  The reference arm
 (``--impl reference``) is unavailable: the reference is a Rust workspace, there is no Rust
 toolchain or network here to build it, and its CUDA path runs none of its kernels for bfloat16
@@ -200,7 +205,7 @@ def prefill_flops(c, layers, lens):
     return layers * (per_layer + attn) + 2 * h * c["vocab_size"] * len(lens)
 
 
-KERNEL_CLASSES = (("products", ("gemm", "skinny")), ("attention", ("attention",)))
+KERNEL_CLASSES = (("products", ("gemm", "skinny")), ("attention", ("attention",)), ("recurrence", ("lightning",)))
 
 
 def prefill_breakdown(eng, step):
@@ -234,7 +239,7 @@ def prefill_breakdown(eng, step):
     out = {"products_ms": 0.0, "attention_ms": 0.0, "other_ms": 0.0}
     for name, e0, e1 in marks:
         cls = next((c for c, keys in KERNEL_CLASSES if any(k in name for k in keys)), "other")
-        out[cls + "_ms"] += e0.elapsed_time(e1)
+        out[cls + "_ms"] = out.get(cls + "_ms", 0.0) + e0.elapsed_time(e1)
     whole = marks[0][1].elapsed_time(marks[-1][2]) if marks else 0.0
     out["gaps_ms"] = max(0.0, whole - sum(out.values()))
     out = {k: round(v, 3) for k, v in out.items()}
@@ -304,6 +309,55 @@ def side_run(a, model, shape_cfg, pk) -> dict:
     return out
 
 
+# layer sizes for the runs of one design beside another (``--design``): width, heads, kv heads, head size, inner size
+DESIGN_SIZES = {"w2048": (2048, 16, 4, 128, 6144), "w2560": (2560, 32, 8, 128, 9728), "w4096": (4096, 32, 8, 128, 12288)}
+DESIGN_VOCAB = 32768
+DESIGN_WINDOW = 1024
+
+
+def datasun_config(width, heads, kv, d, ff, layers):
+    """A Datasun model of these layer sizes: every fourth layer windowed softmax attention, the
+    others lightning attention with head decays between 1 - 2^-5 and 1 - 2^-8."""
+    light = {"heads": heads, "dim": d, "vdim": d, "decay": [1.0 - 2.0 ** -(5.0 + 3.0 * i / max(heads - 1, 1)) for i in range(heads)]}
+    att = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": DESIGN_WINDOW},
+           "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    return {"architecture": "Datasun", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "attention" if i % 4 == 3 else "lightning", "mixer": att if i % 4 == 3 else light, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def design_run(a) -> int:
+    import torch
+    from builderforce_inference_b200 import Model
+    pk = peaks()
+    layers = a.layers or 8
+    clocks = ClockSampler()
+    clocks.start()
+    out = {}
+    for name in (a.sizes.split(",") if a.sizes else sorted(DESIGN_SIZES)):
+        width, heads, kv, d, ff = DESIGN_SIZES[name]
+        configs = {"datasun": datasun_config(width, heads, kv, d, ff, layers),
+                   "qwen3": dict(CONFIG_4B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                                 num_key_value_heads=kv, head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)}
+        for design, cfg in configs.items():
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2048, max_seq_len=CONTEXT, max_batch=64)
+            pf = prefill_run(model, PREFILL_TOKENS, 5, layers, breakdown=True)
+            row = {"prefill_2048": {"ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1), "breakdown": pf["breakdown"]}}
+            for b in (8, 64):
+                decode_run(model, b, 2, 3, seed=3, lens=[1024] * b)
+                r = decode_run(model, b, 32, 3, seed=4, lens=[1024] * b)
+                row[f"decode_b{b}"] = {"tok_s": round(r["tok_s"], 1), "ms_per_step": round(r["ms_per_step"], 4),
+                                       "weight_bytes": int(model.engine.decoder.n_weight_bytes), "launches_per_step": r["launches"] // 32}
+            out.setdefault(name, {})[design] = row
+            del model
+            torch.cuda.empty_cache()
+    print(json.dumps({"workloads": "datasun beside qwen3 at equal layer sizes, builder-run beside the benchmark", "dtype": "bf16",
+                      "layers": layers, "pattern": "lightning x3, attention (window %d) x1" % DESIGN_WINDOW, "vocab": DESIGN_VOCAB,
+                      "peaks": pk["source"], "sizes": out, "clocks": clocks.stop()}))
+    return 0
+
+
 KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456, 2560, 2), "down": (2560, 9728, 1),
                  "head": (151936, 2560, 0)}
 
@@ -350,6 +404,64 @@ def kernel_run(a) -> int:
                 raise SystemExit(f"{a.kernel} does not take M={m} N={n} K={k}")
         bytes_moved, flops = n * k * 2, 2.0 * m * n * k
         what = {"shape": a.shape, "M": m, "N": n, "K": k, "epilogue": epi}
+    elif a.kernel in ("lightning_chunks", "lightning_scan"):
+        # the decayed linear attention: --seqs prompts of --rows tokens (chunks), or --rows sequences of one token (scan)
+        from builderforce_inference_b200.kernels import ops
+        c = CONFIG_4B
+        h, d = c["num_attention_heads"], c["head_dim"]
+        chunks = a.kernel == "lightning_chunks"
+        n_seq, t_new = (a.seqs, a.rows) if chunks else (a.rows, 1)
+        cols = 4 * h * d
+        copies = 1 if chunks else max(2, int(400e6 // (n_seq * h * d * d * 4)) + 1)
+        proj = torch.randn(n_seq * t_new, cols, device=dev, dtype=torch.bfloat16)
+        o = torch.empty(n_seq * t_new, h * d, device=dev, dtype=torch.float32)
+        states = [torch.zeros(n_seq, h, d, d, device=dev, dtype=torch.float32) for _ in range(copies)]
+        decay = torch.linspace(0.96, 0.996, h, device=dev, dtype=torch.float32)
+        cu = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+
+        def one(i):
+            if chunks:
+                if not fast_ops.lightning_chunks_bf16(proj, 0, h * d, 2 * h * d, o, states[0], decay, cu, slots, n_seq, h, d, d):
+                    raise SystemExit("lightning_chunks does not take this shape")
+            else:
+                ops.lightning_scan(proj, 0, h * d, 2 * h * d, o, states[i % copies], decay, cu, slots, n_seq, h, d, d,
+                                   ops.LIGHT_ACT_SILU, True, True)
+        bytes_moved = n_seq * h * d * d * 4 * 2 + n_seq * t_new * (3 * h * d * 2 + h * d * 4)
+        # per token and head: scores and their use within a chunk (causal half of 64 x 64), q S and the state update
+        flops = n_seq * t_new * h * (2.0 * d * d * 2 + (2.0 * 32 * (d + d) if chunks else 0.0))
+        what = {"seqs": n_seq, "new_tokens": t_new, "heads": h, "dim": d, "vdim": d}
+    elif a.kernel == "qk_prepare":
+        # bias, row norm, adjacent-pair rotation over half a head, keys as values, cache write of one prompt of --rows tokens
+        from builderforce_inference_b200.cache import KVView
+        from builderforce_inference_b200.kernels import ops
+        from builderforce_inference_b200.parts.rotary import rotary_table
+        c = CONFIG_4B
+        nq, nkv, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        t = a.rows
+        blocks = (t + 63) // 64
+        table = torch.arange(blocks, dtype=torch.int32, device=dev).reshape(1, blocks)
+        copies = 4
+        kvs = [KVView(torch.zeros(blocks, nkv, 64, d, device=dev, dtype=torch.bfloat16),
+                      torch.zeros(blocks, nkv, 64, d, device=dev, dtype=torch.bfloat16), table, nkv, d, None)
+               for _ in range(copies)]
+        qks = [torch.randn(t, (nq + nkv) * d, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+        bq, bk = (torch.zeros(n * d, device=dev, dtype=torch.bfloat16) for n in (nq, nkv))
+        wq, wk = (torch.ones(n * d, device=dev, dtype=torch.bfloat16) for n in (nq, nkv))
+        res = torch.zeros(t, c["hidden_size"], device=dev)
+        bo = torch.zeros(c["hidden_size"], device=dev, dtype=torch.bfloat16)
+        rope = rotary_table(c["rope_theta"], d // 2, t, dev)
+        pos = torch.arange(t, dtype=torch.int32, device=dev)
+        slot = torch.zeros(t, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def one(i):
+            ops.qk_prepare(qks[i % copies], nq, nkv, d, pos, slot, kvs[i % copies], ops.FLAG_WRITE_CACHE | ops.FLAG_VALUES_ARE_KEYS,
+                           q_bias=bq, k_bias=bk, q_norm_w=wq, k_norm_w=wk, norm_mode=ops.NORM_ROW, eps=1e-6, rope_table=rope,
+                           rot_dim=d // 2, pairing=ops.PAIR_ADJACENT, residual=res, out_bias=bo, status=status)
+        bytes_moved = t * ((2 * nq + 3 * nkv) * d * 2 + 2 * c["hidden_size"] * 4)
+        flops = 0.0
+        what = {"tokens": t, "q_heads": nq, "kv_heads": nkv, "head_dim": d}
     elif a.kernel == "qk_norm_rope":
         # q/k norm + rotation + cache write of one prompt of --rows tokens
         from builderforce_inference_b200.cache import KVView
@@ -544,7 +656,8 @@ def main() -> int:
     ap.add_argument("--timeline-prompt", type=int, default=0, help="with --timeline: a prompt step of this many tokens instead")
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "weight_stream", "qk_norm_rope", "attention_decode",
-                                                       "attention_prefill", "attention_prefill_tcgen05"],
+                                                       "attention_prefill", "attention_prefill_tcgen05", "lightning_chunks", "lightning_scan",
+                                                       "qk_prepare"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")
@@ -561,6 +674,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers of the same sizes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--design", default=None, choices=["datasun"],
+                    help="instead of the benchmark: this design beside qwen3 at equal layer sizes (see design_run)")
+    ap.add_argument("--sizes", default=None, help="with --design: names of DESIGN_SIZES, comma-separated (default: all)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -572,6 +688,8 @@ def main() -> int:
         return timeline_run(a)
     if a.kernel is not None:
         return kernel_run(a)
+    if a.design is not None:
+        return design_run(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for --gpus {a.gpus})")
         return 2

@@ -174,5 +174,39 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// The gated activation of a feed-forward, as the matrix products' gated epilogue applies it to a
+// (gate, up) pair: with g' = min(g, limit) and u' = clamp(u, -limit, limit) (limit <= 0: no clamping)
+//     g' * sigmoid(alpha * g') * (u' + shift)
+// alpha 1, no limit and shift 0 is SiLU(gate) * up, and evaluates to the same bits as that formula.
+// A library holds ONE set of constants per host thread (bfi_set_gate), which every product launched
+// from that thread with the gated epilogue takes along as a kernel argument.
+struct GateAct {
+    float alpha, limit, shift;
+};
+extern thread_local GateAct g_bfi_gate;
+
+__device__ __forceinline__ float gate_mul_exact(float g, float u, const GateAct a) {
+    if (a.limit > 0.0f) {
+        g = fminf(g, a.limit);
+        u = fminf(fmaxf(u, -a.limit), a.limit);
+    }
+    const float z = a.alpha * g;
+    float s;                       // overflow-safe two-branch sigmoid
+    if (z >= 0.0f) {
+        s = 1.0f / (1.0f + expf(-z));
+    } else {
+        const float e = expf(z);
+        s = e / (1.0f + e);
+    }
+    return g * s * (u + a.shift);
+}
+__device__ __forceinline__ float gate_mul_fast(float g, float u, const GateAct a) {
+    if (a.limit > 0.0f) {
+        g = fminf(g, a.limit);
+        u = fminf(fmaxf(u, -a.limit), a.limit);
+    }
+    return __fdividef(g, 1.0f + __expf(-a.alpha * g)) * (u + a.shift);
+}
+
 static inline int dtype_size(int dtype) { return dtype == BFI_F32 ? 4 : 2; }
 static inline bool dtype_ok(int dtype) { return dtype == BFI_F32 || dtype == BFI_BF16; }

@@ -31,6 +31,14 @@ extern "C" int bfi_set_pdl(int on) {
     return 0;
 }
 
+// The constants of the gated epilogue for the products this host thread launches from now on.
+thread_local GateAct g_bfi_gate = {1.0f, 0.0f, 0.0f};
+
+extern "C" int bfi_set_gate(float alpha, float limit, float shift) {
+    g_bfi_gate.alpha = alpha, g_bfi_gate.limit = limit, g_bfi_gate.shift = shift;
+    return 0;
+}
+
 // Multiprocessors of the current device, asked of the driver once per device: launchers size
 // their grids and work splits by it instead of by a constant.
 int bfi_sm_count() {

@@ -37,7 +37,7 @@ __device__ __forceinline__ float silu_mul_f32(float g, float u) {
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 gemm_tile_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
-                 int c_dtype, long ldc, int M, int N, int K, int epilogue) {
+                 int c_dtype, long ldc, int M, int N, int K, int epilogue, GateAct gate) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) float As[TK][TM + TPAD];
@@ -95,7 +95,7 @@ gemm_tile_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, l
             for (int j = 0; j < 4; j += 2) {
                 const int gn = n0 + tx * 4 + j;
                 if (gn + 1 < N)
-                    store_from_f32(C, c_dtype, (size_t)gm * ldc + (gn >> 1), silu_mul_f32(acc[i][j], acc[i][j + 1]));
+                    store_from_f32(C, c_dtype, (size_t)gm * ldc + (gn >> 1), gate_mul_exact(acc[i][j], acc[i][j + 1], gate));
             }
         } else {
 #pragma unroll
@@ -120,7 +120,7 @@ gemm_tile_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, l
 template <typename TA, typename TW, int MB>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
-                 int c_dtype, long ldc, int m_base, int M, int N, int K, int epilogue) {
+                 int c_dtype, long ldc, int m_base, int M, int N, int K, int epilogue, GateAct gate) {
     pdl_trigger();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,7 +155,7 @@ gemv_rows_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, l
             const int gm = m_base + m;
             if (gm >= M) continue;
             if (epilogue == EPI_SWIGLU) {
-                if (has_b) store_from_f32(C, c_dtype, (size_t)gm * ldc + (n_a >> 1), silu_mul_f32(acc_a[m], acc_b[m]));
+                if (has_b) store_from_f32(C, c_dtype, (size_t)gm * ldc + (n_a >> 1), gate_mul_exact(acc_a[m], acc_b[m], gate));
             } else if (epilogue == EPI_ACCUMULATE) {
                 reinterpret_cast<float*>(C)[(size_t)gm * ldc + n_a] += acc_a[m];
                 if (has_b) reinterpret_cast<float*>(C)[(size_t)gm * ldc + n_b] += acc_b[m];
@@ -178,23 +178,23 @@ static int launch_simt(const void* A, long lda, const void* W, long ldw, void* C
             const int left = M - m_base;
             if (left >= 5)
                 bfi_launch(gemv_rows_kernel<TA, TW, 8>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
-                                                                              c_dtype, ldc, m_base, M, N, K, epilogue);
+                                                                              c_dtype, ldc, m_base, M, N, K, epilogue, g_bfi_gate);
             else if (left >= 3)
                 bfi_launch(gemv_rows_kernel<TA, TW, 4>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
-                                                                              c_dtype, ldc, m_base, M, N, K, epilogue);
+                                                                              c_dtype, ldc, m_base, M, N, K, epilogue, g_bfi_gate);
             else if (left == 2)
                 bfi_launch(gemv_rows_kernel<TA, TW, 2>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
-                                                                              c_dtype, ldc, m_base, M, N, K, epilogue);
+                                                                              c_dtype, ldc, m_base, M, N, K, epilogue, g_bfi_gate);
             else
                 bfi_launch(gemv_rows_kernel<TA, TW, 1>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
-                                                                              c_dtype, ldc, m_base, M, N, K, epilogue);
+                                                                              c_dtype, ldc, m_base, M, N, K, epilogue, g_bfi_gate);
         }
         return bfi_check_launch("gemv_rows");
     }
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     BFI_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d is too large for one launch", M);
     bfi_launch(gemm_tile_kernel<TA, TW>, dim3(grid), dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C, c_dtype, ldc, M, N, K,
-                                                      epilogue);
+                                                      epilogue, g_bfi_gate);
     return bfi_check_launch("gemm_tile");
 }
 

@@ -56,7 +56,7 @@ template <int BT>
 __global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int kblocks_per_split,
-                    int epilogue, int* __restrict__ status, TcWaits waits) {
+                    int epilogue, GateAct gate, int* __restrict__ status, TcWaits waits) {
     using Cfg = TcConfig<BT>;
     const uint32_t spin_limit = waits.spin_limit;
     extern __shared__ unsigned char smem_raw[];
@@ -209,7 +209,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 tmem_ld16(lane_addr + c * 16, v);
                 if (epilogue == EPI_SWIGLU) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = silu_mul_tc(v[j], __shfl_down_sync(0xffffffffu, v[j], 1));
+                    for (int j = 0; j < 16; ++j) v[j] = gate_mul_fast(v[j], __shfl_down_sync(0xffffffffu, v[j], 1), gate);
                     if ((lane & 1) == 0 && n + 1 < N) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
@@ -282,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int r = 0; r < 8; ++r) v += x[u][r];
                     if (epilogue == EPI_SWIGLU) {
-                        const float act = silu_mul_tc(v, __shfl_down_sync(0xffffffffu, v, 1));
+                        const float act = gate_mul_fast(v, __shfl_down_sync(0xffffffffu, v, 1), gate);
                         if (live && (lane & 1) == 0 && n + 1 < N) store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), act);
                     } else if (live && n < N) {
                         const size_t o = (size_t)m * ldc + n;
@@ -344,7 +344,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // staging tile, and the warp then writes (or, adding, reads and writes) whole rows: 8 lanes a row.
 // G = 2 for float32 outputs, 4 for bfloat16 and for the gated epilogue.
 template <int G>
-__device__ __forceinline__ void tp_emit_group(uint4* stage, const float (&v)[G][16], int lane, int epilogue, int c_dtype,
+__device__ __forceinline__ void tp_emit_group(uint4* stage, const float (&v)[G][16], int lane, int epilogue, GateAct gate, int c_dtype,
                                               void* __restrict__ C, long ldc, int m_base, int M, int n0) {
     uint4 piece[8];
     int n_pieces;
@@ -357,8 +357,8 @@ __device__ __forceinline__ void tp_emit_group(uint4* stage, const float (&v)[G][
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(silu_mul_tc(v[g][4 * j], v[g][4 * j + 1]),
-                                                              silu_mul_tc(v[g][4 * j + 2], v[g][4 * j + 3]));
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(gate_mul_fast(v[g][4 * j], v[g][4 * j + 1], gate),
+                                                              gate_mul_fast(v[g][4 * j + 2], v[g][4 * j + 3], gate));
                     pk[j] = *reinterpret_cast<uint32_t*>(&t2);
                 }
                 piece[g] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -370,10 +370,10 @@ __device__ __forceinline__ void tp_emit_group(uint4* stage, const float (&v)[G][
             for (int g = 0; g < G; ++g)
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
-                    piece[(2 * g + q) & 7] = make_uint4(__float_as_uint(silu_mul_tc(v[g][8 * q], v[g][8 * q + 1])),
-                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 2], v[g][8 * q + 3])),
-                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 4], v[g][8 * q + 5])),
-                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 6], v[g][8 * q + 7])));
+                    piece[(2 * g + q) & 7] = make_uint4(__float_as_uint(gate_mul_fast(v[g][8 * q], v[g][8 * q + 1], gate)),
+                                                        __float_as_uint(gate_mul_fast(v[g][8 * q + 2], v[g][8 * q + 3], gate)),
+                                                        __float_as_uint(gate_mul_fast(v[g][8 * q + 4], v[g][8 * q + 5], gate)),
+                                                        __float_as_uint(gate_mul_fast(v[g][8 * q + 6], v[g][8 * q + 7], gate)));
             out_byte0 = (size_t)(n0 >> 1) * 4;
         }
     } else if (c_dtype == BFI_BF16) {     // two pieces per chunk
@@ -443,7 +443,8 @@ template <int HALVES>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                             void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int tiles_m, int tiles_n,
-                            int tile_n, int n_stages, int epilogue, int vec_ok, int* __restrict__ status, TcWaits waits) {
+                            int tile_n, int n_stages, int epilogue, GateAct gate, int vec_ok, int* __restrict__ status,
+                            TcWaits waits) {
     const uint32_t spin_limit = waits.spin_limit;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -634,12 +635,12 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     if (!wide && c_direct + 4 <= c_end && n0 + 64 <= N) {
                         float v[4][16];
                         tmem_ld64(taddr + c_direct * 16, v);
-                        tp_emit_group<4>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
+                        tp_emit_group<4>(stage, v, lane, epilogue, gate, c_dtype, C, ldc, m_base, M, n0);
                         c_direct += 4;
                     } else if (c_direct + 2 <= c_end && n0 + 32 <= N) {
                         float v[2][16];
                         tmem_ld32(taddr + c_direct * 16, v);
-                        tp_emit_group<2>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
+                        tp_emit_group<2>(stage, v, lane, epilogue, gate, c_dtype, C, ldc, m_base, M, n0);
                         c_direct += 2;
                     } else {
                         break;
@@ -661,8 +662,8 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         for (int j = 0; j < 4; ++j)
                             pk[j] = c_dtype == BFI_BF16
                                         ? ([&] {
-                                              __nv_bfloat162 t2 = __floats2bfloat162_rn(silu_mul_tc(v[4 * j], v[4 * j + 1]),
-                                                                                        silu_mul_tc(v[4 * j + 2], v[4 * j + 3]));
+                                              __nv_bfloat162 t2 = __floats2bfloat162_rn(gate_mul_fast(v[4 * j], v[4 * j + 1], gate),
+                                                                                        gate_mul_fast(v[4 * j + 2], v[4 * j + 3], gate));
                                               return *reinterpret_cast<uint32_t*>(&t2);
                                           })()
                                         : 0u;
@@ -672,13 +673,13 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                         } else {
                             float* o = reinterpret_cast<float*>(C) + (size_t)m * ldc + (n >> 1);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) o[j] = silu_mul_tc(v[2 * j], v[2 * j + 1]);
+                            for (int j = 0; j < 8; ++j) o[j] = gate_mul_fast(v[2 * j], v[2 * j + 1], gate);
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 16; j += 2)
                             if (n + j + 1 < N)
-                                store_from_f32(C, c_dtype, (size_t)m * ldc + ((n + j) >> 1), silu_mul_tc(v[j], v[j + 1]));
+                                store_from_f32(C, c_dtype, (size_t)m * ldc + ((n + j) >> 1), gate_mul_fast(v[j], v[j + 1], gate));
                     }
                 } else if (epilogue == EPI_ACCUMULATE) {
                     float* o = reinterpret_cast<float*>(C) + (size_t)m * ldc + n;
@@ -887,7 +888,7 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, ma, C, c_dtype, ldc, M, N, K, p.kblocks_per_split, epilogue, status, waits);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, ma, C, c_dtype, ldc, M, N, K, p.kblocks_per_split, epilogue, g_bfi_gate, status, waits);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return bfi_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
@@ -953,10 +954,10 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
     const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
     if (halves == 2)
         bfi_launch(gemm_tcgen05_prefill_kernel<2>, dim3(grid), dim3(TP_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
-                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, g_bfi_gate, vec_ok, status, waits);
     else
         bfi_launch(gemm_tcgen05_prefill_kernel<1>, dim3(grid), dim3(TP_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
-                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, g_bfi_gate, vec_ok, status, waits);
     return bfi_check_launch("gemm_tcgen05_prefill");
 }
 

@@ -88,6 +88,89 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, long stride, i
         for (int d = g; d < D; d += ng) sp[(size_t)d * V + c] = S[d * vb + c];
 }
 
+// One new token per sequence: the state never rests in shared memory.  A block owns 32 columns of
+// one head of one sequence; thread (g, c) holds rows g, g + 8, ... of column c in registers, all of
+// them asked for before the wait for the kernel that makes q, k and v (the state was left by an
+// earlier step), so that a step's traffic, which is the states read and written once, streams.
+#define LIGHT_STEP_COLS 32
+#define LIGHT_STEP_GROUPS 8
+
+template <typename T, int RPT>
+__global__ void __launch_bounds__(LIGHT_STEP_COLS * LIGHT_STEP_GROUPS)
+lightning_step_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
+                      long out_stride, float* __restrict__ state, const float* __restrict__ decay,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int H, int D, int V,
+                      int v_blocks, int act) {
+    pdl_trigger();
+    __shared__ float qs[LIGHT_STEP_GROUPS * RPT], ks[LIGHT_STEP_GROUPS * RPT];
+    __shared__ float red[LIGHT_STEP_GROUPS][LIGHT_STEP_COLS];
+    const int seq = blockIdx.y;
+    const int slot = seq_slot[seq];
+    if (slot < 0) return;
+    const int h = blockIdx.x / v_blocks;
+    const int v0 = (blockIdx.x - h * v_blocks) * LIGHT_STEP_COLS;
+    const int c = threadIdx.x & (LIGHT_STEP_COLS - 1), g = threadIdx.x / LIGHT_STEP_COLS;
+    const bool col_ok = v0 + c < V;
+    const float w = decay[h];
+    float* sp = state + (((size_t)slot * H + h) * D) * V + v0 + c;
+    float S[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int d = g + LIGHT_STEP_GROUPS * i;
+        S[i] = (col_ok && d < D) ? sp[(size_t)d * V] : 0.0f;
+    }
+    pdl_wait();
+    const int t = cu_seqlens[seq];
+    const T* row = proj + (size_t)t * stride;
+    for (int j = threadIdx.x; j < D; j += blockDim.x) {
+        const float qv = to_f32(row[q_off + (size_t)h * D + j]), kv = to_f32(row[k_off + (size_t)h * D + j]);
+        qs[j] = act == LIGHT_ACT_SILU ? light_silu(qv) : qv;
+        ks[j] = act == LIGHT_ACT_SILU ? light_silu(kv) : kv;
+    }
+    float vv = 0.0f;
+    if (col_ok) {
+        vv = to_f32(row[v_off + (size_t)h * V + v0 + c]);
+        if (act == LIGHT_ACT_SILU) vv = light_silu(vv);
+    }
+    __syncthreads();
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int d = g + LIGHT_STEP_GROUPS * i;
+        if (d < D) {
+            const float s = fmaf(w, S[i], ks[d] * vv);
+            if (col_ok) sp[(size_t)d * V] = s;
+            acc = fmaf(s, qs[d], acc);
+        }
+    }
+    red[g][c] = acc;
+    __syncthreads();
+    if (g == 0 && col_ok) {
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < LIGHT_STEP_GROUPS; ++i) o += red[i][c];
+        out[(size_t)t * out_stride + (size_t)h * V + v0 + c] = o;
+    }
+}
+
+template <typename T>
+static bool launch_light_step(const void* proj, long stride, int q_off, int k_off, int v_off, float* out, long out_stride,
+                              float* state, const float* decay, const int* cu_seqlens, const int* seq_slot, int n_seqs,
+                              int H, int D, int V, int act, cudaStream_t stream) {
+    const int v_blocks = (V + LIGHT_STEP_COLS - 1) / LIGHT_STEP_COLS;
+    const dim3 grid(H * v_blocks, n_seqs), block(LIGHT_STEP_COLS * LIGHT_STEP_GROUPS);
+#define BFI_LIGHT_STEP(R)                                                                                              \
+    bfi_launch(lightning_step_kernel<T, R>, grid, block, 0, stream, (const T*)proj, stride, q_off, k_off, v_off, out,  \
+               out_stride, state, decay, cu_seqlens, seq_slot, H, D, V, v_blocks, act)
+    if (D <= 32) BFI_LIGHT_STEP(4);
+    else if (D <= 64) BFI_LIGHT_STEP(8);
+    else if (D <= 128) BFI_LIGHT_STEP(16);
+    else if (D <= 256) BFI_LIGHT_STEP(32);
+    else return false;
+#undef BFI_LIGHT_STEP
+    return true;
+}
+
 extern "C" int bfi_lightning_scan(const void* proj, int dtype, long stride, int q_off, int k_off, int v_off, float* out,
                                   long out_stride, float* state, const float* decay, const int* cu_seqlens,
                                   const int* seq_slot, int n_seqs, int H, int D, int V, int act, int few_tokens,
@@ -97,6 +180,12 @@ extern "C" int bfi_lightning_scan(const void* proj, int dtype, long stride, int 
     BFI_REQUIRE(act == LIGHT_ACT_NONE || act == LIGHT_ACT_SILU, "lightning_scan: unknown activation %d", act);
     BFI_REQUIRE(out_stride >= (long)H * V, "lightning_scan: output stride shorter than the heads");
     if (n_seqs <= 0) return 0;
+    if (few_tokens == 2 && n_seqs <= 65535) {      // every sequence brings exactly one token: the state stays in registers
+        const bool ran = dtype == BFI_F32
+            ? launch_light_step<float>(proj, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, act, stream)
+            : launch_light_step<bf16>(proj, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, act, stream);
+        if (ran) return bfi_check_launch("lightning_step");
+    }
     // columns per block: few where the step is short (more blocks share the state's traffic)
     int vb = V;
     const int want = few_tokens ? 32 : 64;

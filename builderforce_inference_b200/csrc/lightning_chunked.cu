@@ -22,7 +22,7 @@ using namespace nvcuda;
 #define LC 64          // tokens per chunk
 #define LC_WARPS 8
 
-__device__ __forceinline__ float lc_silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float lc_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 struct LcSmem {
     int ldq, ldv, lda, ldaf, ldof, ldsf;
@@ -99,30 +99,65 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
     }
     pdl_wait();
 
+    // A chunk's q, k (all of the head) and v (this block's columns) travel as 16-byte pieces: a thread
+    // asks for the next chunk's pieces before it works on this one, and activates and stores them
+    // when their turn comes, so the trip to memory hides behind a chunk's products.
+    const int D8 = D >> 3;
+    constexpr int VB8 = VB / 8;
+    constexpr int NQ = 4, NV = (LC * VB8 + LC_WARPS * 32 - 1) / (LC_WARPS * 32);
+    uint4 rq[NQ], rk[NQ], rv[NV];
+    auto fetch = [&](int c0) {
+        const int n = min(LC, nt - c0);
+#pragma unroll
+        for (int u = 0; u < NQ; ++u) {
+            const int idx = tid + u * LC_WARPS * 32, t = idx / D8, e = idx - t * D8;
+            rq[u] = rk[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (t < n) {
+                const bf16* row = proj + (size_t)(t0 + c0 + t) * stride + (size_t)h * D + e * 8;
+                rq[u] = *reinterpret_cast<const uint4*>(row + q_off);
+                rk[u] = *reinterpret_cast<const uint4*>(row + k_off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int idx = tid + u * LC_WARPS * 32, t = idx / VB8, e = idx - t * VB8;
+            rv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (t < n)
+                rv[u] = *reinterpret_cast<const uint4*>(proj + (size_t)(t0 + c0 + t) * stride + v_off + (size_t)h * V + v0 + e * 8);
+        }
+    };
+    auto activate = [](uint4 raw) {
+        uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+            const __nv_bfloat162 y = __floats2bfloat162_rn(lc_silu(__low2float(x)), lc_silu(__high2float(x)));
+            w[j] = *reinterpret_cast<const uint32_t*>(&y);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    };
+    auto stash = [&]() {
+#pragma unroll
+        for (int u = 0; u < NQ; ++u) {
+            const int idx = tid + u * LC_WARPS * 32, t = idx / D8, e = idx - t * D8;
+            if (t < LC) {
+                *reinterpret_cast<uint4*>(Qs + t * L.ldq + e * 8) = activate(rq[u]);
+                *reinterpret_cast<uint4*>(Ks + t * L.ldq + e * 8) = activate(rk[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int idx = tid + u * LC_WARPS * 32, t = idx / VB8, e = idx - t * VB8;
+            if (t < LC) *reinterpret_cast<uint4*>(Vs + t * L.ldv + e * 8) = activate(rv[u]);
+        }
+    };
+    fetch(0);
+
     for (int c0 = 0; c0 < nt; c0 += LC) {
         const int n = min(LC, nt - c0);
-        // ---- the chunk's q, k (all of the head) and v (this block's columns), activated, as bfloat16
-        for (int i = tid; i < LC * (D / 2); i += blockDim.x) {
-            const int t = i / (D / 2), e = (i - t * (D / 2)) * 2;
-            __nv_bfloat162 qv = __floats2bfloat162_rn(0.0f, 0.0f), kv = qv;
-            if (t < n) {
-                const bf16* row = proj + (size_t)(t0 + c0 + t) * stride + (size_t)h * D + e;
-                const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162*>(row + q_off);
-                const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(row + k_off);
-                qv = __floats2bfloat162_rn(lc_silu(__low2float(q2)), lc_silu(__high2float(q2)));
-                kv = __floats2bfloat162_rn(lc_silu(__low2float(k2)), lc_silu(__high2float(k2)));
-            }
-            *reinterpret_cast<__nv_bfloat162*>(Qs + t * L.ldq + e) = qv;
-            *reinterpret_cast<__nv_bfloat162*>(Ks + t * L.ldq + e) = kv;
-        }
-        for (int i = tid; i < LC * VB; i += blockDim.x) {
-            const int t = i / VB, c = i - t * VB;
-            float x = 0.0f;
-            if (t < n && v0 + c < V)
-                x = lc_silu(__bfloat162float(proj[(size_t)(t0 + c0 + t) * stride + v_off + (size_t)h * V + v0 + c]));
-            Vs[t * L.ldv + c] = __float2bfloat16_rn(x);
-        }
+        stash();
         __syncthreads();
+        if (c0 + LC < nt) fetch(c0 + LC);
 
         // ---- scores q k^T (tiles at or below the diagonal) and q S
         const int n_a = CT * (CT + 1) / 2, n_o = CT * VT;
@@ -245,9 +280,9 @@ extern "C" int bfi_lightning_chunks_bf16(const void* proj, long stride, int q_of
     BFI_REQUIRE(H > 0 && D > 0 && V > 0, "lightning_chunks: bad sizes heads=%d dim=%d vdim=%d", H, D, V);
     BFI_REQUIRE(out_stride >= (long)H * V, "lightning_chunks: output stride shorter than the heads");
     if (n_seqs <= 0) return 0;
-    if (D % 16 != 0 || V % 16 != 0 || n_seqs > 65535) return 2;
-    // q and k are read as pairs: their columns must start on 4-byte boundaries
-    if (((uintptr_t)proj & 3) != 0 || stride % 2 != 0 || q_off % 2 != 0 || k_off % 2 != 0) return 2;
+    if (D % 16 != 0 || D > 128 || V % 16 != 0 || n_seqs > 65535) return 2;
+    // q, k and v are read in 16-byte pieces
+    if (((uintptr_t)proj & 15) != 0 || stride % 8 != 0 || q_off % 8 != 0 || k_off % 8 != 0 || v_off % 8 != 0) return 2;
     // columns per block: as many as fit shared memory, fewer when that is needed to fill the GPU
     const size_t limit = 200 * 1024;
     int vb = 0;

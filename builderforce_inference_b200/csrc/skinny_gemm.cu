@@ -61,7 +61,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 template <int NT, int RT, int U>
 __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const bf16* __restrict__ W, long ldw,
                                    void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int k_per_warp,
-                                   int epilogue, int prefetch, int ksplit, float* __restrict__ scratch,
+                                   int epilogue, GateAct gate, int prefetch, int ksplit, float* __restrict__ scratch,
                                    int* __restrict__ counters) {
     extern __shared__ float red[];   // [warps][RT*16][NT*8 + 1]
     constexpr int R = RT * 16;
@@ -217,7 +217,7 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
             const int m = idx / PAIRS, p = idx - m * PAIRS;
             const int row = row0 + 2 * p;
             if (m >= M || row + 1 >= N) continue;
-            store_from_f32(C, c_dtype, (size_t)m * ldc + (row >> 1), silu_mul_fast(total(2 * p, m), total(2 * p + 1, m)));
+            store_from_f32(C, c_dtype, (size_t)m * ldc + (row >> 1), gate_mul_fast(total(2 * p, m), total(2 * p + 1, m), gate));
         }
     } else {
         for (int idx = threadIdx.x; idx < R * MP; idx += blockDim.x) {
@@ -302,7 +302,7 @@ static int launch_skinny(const bf16* A, long lda, const bf16* W, long ldw, void*
                                               cudaGetErrorString(e));
     }
     bfi_launch(kernel, dim3(p.tiles, p.ksplit), dim3(p.warps * 32), p.smem, stream, A, lda, W, ldw, C, c_dtype, ldc, M, N,
-               K, p.k_per_warp, epilogue, g_tune_prefetch, p.ksplit, scratch, counters);
+               K, p.k_per_warp, epilogue, g_bfi_gate, g_tune_prefetch, p.ksplit, scratch, counters);
     return bfi_check_launch("skinny_gemm");
 }
 

@@ -24,8 +24,27 @@ def _fast_ops():
     return _fast
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
-    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+def _set_gate(fast: bool, alpha: float, limit: float, shift: float) -> None:
+    from ctypes import c_float
+
+    from .library import library
+    for name in (("core", "fast") if fast else ("core",)):
+        library(name).lib.bfi_set_gate(c_float(alpha), c_float(limit), c_float(shift))
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, gate=None) -> None:
+    """``gate``: with the gated epilogue, the activation's constants ``(alpha, limit, shift)``:
+    ``g' * sigmoid(alpha * g') * (u' + shift)`` with gate and up clamped at ``limit`` (0: not
+    clamped); None is SiLU(gate) * up.  The kernels take them along as launch arguments."""
+    fast = a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if gate is not None and epilogue == EPI_SWIGLU:
+        _set_gate(fast, *gate)
+        try:
+            linear(a, w, out, epilogue)
+        finally:
+            _set_gate(fast, 1.0, 0.0, 0.0)
+        return
+    if fast:
         if _fast_ops().linear_bf16(a, w, out, epilogue):
             return
     ops.gemm_simt(a, w, out, epilogue)

@@ -258,11 +258,13 @@ LIGHT_ACT_NONE, LIGHT_ACT_SILU = 0, 1
 
 def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: torch.Tensor, state: torch.Tensor,
                    decay: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
-                   n_heads: int, dim: int, vdim: int, act: int = LIGHT_ACT_SILU, few_tokens: bool = False) -> None:
+                   n_heads: int, dim: int, vdim: int, act: int = LIGHT_ACT_SILU, few_tokens: bool = False,
+                   single_tokens: bool = False) -> None:
     """Linear attention with a decay per head over the step's new tokens, sequence by sequence:
     ``S = decay * S + k v^T; o = S^T q`` with ``S`` float32 ``[slots, heads, dim, vdim]`` carried
     in ``state``.  q, k, v are columns ``q_off``, ``k_off``, ``v_off`` of ``proj`` (activated here
-    when ``act`` says so); ``out`` is float32 ``[tokens, heads * vdim]``."""
+    when ``act`` says so); ``out`` is float32 ``[tokens, heads * vdim]``.  ``single_tokens``: every
+    sequence of the step brings exactly one token (the kernel then keeps the state in registers)."""
     _need_cuda(proj, out, state, decay, cu_seqlens, seq_slot)
     _rows_2d(proj, "projections")
     _rows_2d(out, "recurrence output")
@@ -279,7 +281,7 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, out: 
     library("core").call("bfi_lightning_scan", _ptr(proj), c_int(dtype_code(proj.dtype)), c_long(proj.stride(0)),
                          c_int(q_off), c_int(k_off), c_int(v_off), _ptr(out), c_long(out.stride(0)), _ptr(state),
                          _ptr(decay), _ptr(cu_seqlens), _ptr(seq_slot), c_int(n_seqs), c_int(n_heads), c_int(dim),
-                         c_int(vdim), c_int(act), c_int(1 if few_tokens else 0), _stream())
+                         c_int(vdim), c_int(act), c_int(2 if single_tokens else (1 if few_tokens else 0)), _stream())
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:

@@ -77,4 +77,5 @@ class LightningAttention(Mixer):
                     self.n_heads, self.dim, self.vdim):
                 return
         ops.lightning_scan(proj, 0, qk, 2 * qk, o, state, self.decay, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
-                           self.n_heads, self.dim, self.vdim, ops.LIGHT_ACT_SILU, few_tokens=ctx.max_seq_tokens == 1)
+                           self.n_heads, self.dim, self.vdim, ops.LIGHT_ACT_SILU, few_tokens=ctx.max_seq_tokens == 1,
+                           single_tokens=ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs)

@@ -2,7 +2,7 @@
 (crates/bfi-models/src/qwen3.rs:244-250; SiLU*mul crates/bfi-core/src/cpu.rs:169-180).
 
 The gate and up matrices are stored interleaved row by row (gate_j, up_j, gate_j+1, ...), so
-one matrix product yields both and its epilogue applies SiLU*mul while the pair is still in
+one matrix product yields both and its epilogue applies the activation while the pair is still in
 registers; the down product adds into the residual stream.
 
 The activation is a family with three constants: with ``g' = min(g, limit)`` and
@@ -16,8 +16,7 @@ from typing import Dict
 
 import torch
 
-from ..kernels import ops
-from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, EPI_SWIGLU, linear
+from ..kernels.linear import EPI_ACCUMULATE, EPI_SWIGLU, linear
 from .base import FEED_FORWARDS, FeedForward, ParamSpec
 
 
@@ -50,10 +49,6 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, h, residual) -> None:
         act = ctx.rows("mlp.act", self.inner)
-        if self.plain_silu:
-            linear(h, self.w_gate_up, act, EPI_SWIGLU)
-        else:
-            pairs = ctx.rows("mlp.pairs", 2 * self.inner)
-            linear(h, self.w_gate_up, pairs, EPI_STORE)
-            ops.gate_mul(pairs, act, True, self.gate_alpha, self.limit or 0.0, self.up_shift)
+        gate = None if self.plain_silu else (self.gate_alpha, self.limit or 0.0, self.up_shift)
+        linear(h, self.w_gate_up, act, EPI_SWIGLU, gate)
         linear(act, self.w_down, residual, EPI_ACCUMULATE)

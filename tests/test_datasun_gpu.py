@@ -335,7 +335,7 @@ def scan(proj, state, decay, seqs, H, D, V, few=False):
         cu.append(cu[-1] + n)
     o = torch.full((cu[-1], H * V), float("nan"), dtype=F32, device=DEV)
     ops().lightning_scan(proj, 0, H * D, 2 * H * D, o, state, decay, i32(cu), i32([s for s, _ in seqs]), len(seqs), H, D, V,
-                         ops().LIGHT_ACT_SILU, few)
+                         ops().LIGHT_ACT_SILU, few, few and all(n == 1 for _, n in seqs))
     return o.double().cpu()
 
 
@@ -491,6 +491,34 @@ def test_gate_mul_clamps_and_shifts(dt):
         ref = P.clamped_gate(x[:, 0::2].double(), x[:, 1::2].double(), limit, alpha, shift)
         assert rel_err(out.double().cpu(), ref) < (1e-6 if dt == F32 else 6e-3)
     assert float(x.abs().max()) > 2.5                    # the clamps had something to do
+
+
+@pytest.mark.parametrize("dt", [F32, BF16])
+def test_feed_forward_part_applies_the_clamped_gate_in_every_product_kernel(dt):
+    """Few rows, many rows and 128+ rows take different matrix-product kernels; each applies the gate
+    in its epilogue.  The plain SiLU form beside it must stay what it was."""
+    from builderforce_inference_b200.engine.context import Workspace, build_context
+    from builderforce_inference_b200.engine.decoder import Runtime
+    from builderforce_inference_b200.parts import FEED_FORWARDS, PartSpec
+    rt, ws = Runtime(DEV, dt), Workspace(DEV)
+    width, inner = 96, 160
+    g = torch.Generator().manual_seed(2)
+    w = {"gate_proj": torch.randn(inner, width, generator=g) * 0.3, "up_proj": torch.randn(inner, width, generator=g) * 0.3,
+         "down_proj": torch.randn(width, inner, generator=g) * 0.1}
+    w = {k: v.to(dt) for k, v in w.items()}
+    for params, (limit, slope, shift) in (({"gate_alpha": 1.702, "limit": 0.8, "up_shift": 1.0}, (0.8, 1.702, 1.0)),
+                                          ({}, (None, 1.0, 0.0)), ({"gate_alpha": 0.5, "up_shift": -0.5}, (None, 0.5, -0.5))):
+        ffn = FEED_FORWARDS.build(PartSpec("gated_mlp", dict(width=width, inner=inner, **params)))
+        ffn.load_all({k: v.to(DEV) for k, v in w.items()}, rt)
+        for rows in (1, 5, 40, 130, 300):
+            h = torch.randn(rows, width, generator=g).to(dt)
+            res = torch.randn(rows, width, generator=g)
+            out = res.clone().to(DEV)
+            ffn.forward(build_context([(0, 0, [1] * rows)], dt, ws, DEV), h.to(DEV), out)
+            f = {k: v.double() for k, v in w.items()}
+            act = P.clamped_gate(h.double() @ f["gate_proj"].t(), h.double() @ f["up_proj"].t(), limit, slope, shift)
+            ref = res.double() + act @ f["down_proj"].t()
+            assert rel_err(out, ref) < (5e-6 if dt == F32 else 1.5e-2), (params, rows)
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
