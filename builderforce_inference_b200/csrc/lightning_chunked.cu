@@ -12,15 +12,12 @@
 // 16 bits of mantissa; the master copy of the state stays float32 and is only ever added to.
 //
 // A block owns VB columns of one head of one sequence and walks the sequence's chunks in order;
-// the matrix products are 16x16x16 tiles dealt round-robin to its 8 warps.
-#include <mma.h>
-
-#include "common.cuh"
-
-using namespace nvcuda;
+// the matrix products are 16x16 tiles of mma.sync.m16n8k16 (operands by ldmatrix) dealt round-robin to
+// its 8 warps.
+#include "attention_tiles.cuh"
 
 #define LC 64          // tokens per chunk
-#define LC_WARPS 8
+#define LC_WARPS 8      // (AD_WARPS of attention_tiles.cuh belongs to the attention kernels)
 
 __device__ __forceinline__ float lc_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -51,18 +48,59 @@ static __host__ __device__ inline LcSmem lc_layout(int D, int VB) {
     return s;
 }
 
+// Operands of mma.sync.m16n8k16 out of shared memory by ldmatrix, for a 16x16 tile of the result (two
+// blocks of 8 columns: b[0], b[1] feed the first, b[2], b[3] the second).  "rows": the tile lies
+// as it is multiplied (A as [m][k], B as [k][n]); "cols": it lies transposed (A as [k][m], B as [n][k]).
+__device__ __forceinline__ void lc_a_rows(uint32_t (&a)[4], const bf16* tile, int ld) {
+    const int lane = threadIdx.x & 31;
+    ldmatrix_x4(a, tile + (lane & 15) * ld + (lane >> 4) * 8);
+}
+__device__ __forceinline__ void lc_a_cols(uint32_t (&a)[4], const bf16* tile, int ld) {
+    const int lane = threadIdx.x & 31;
+    ldmatrix_x4_trans(a, tile + ((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8);
+}
+__device__ __forceinline__ void lc_b_rows(uint32_t (&b)[4], const bf16* tile, int ld) {
+    const int lane = threadIdx.x & 31;
+    ldmatrix_x4_trans(b, tile + (lane & 15) * ld + (lane >> 4) * 8);
+}
+__device__ __forceinline__ void lc_b_cols(uint32_t (&b)[4], const bf16* tile, int ld) {
+    const int lane = threadIdx.x & 31;
+    ldmatrix_x4(b, tile + ((lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8);
+}
+// The 16x16 float32 tile of a warp's accumulators to and from shared memory.
+__device__ __forceinline__ void lc_store(float* tile, int ld, const float (&acc)[2][4]) {
+    const int g = (threadIdx.x & 31) >> 2, t = threadIdx.x & 3;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+        *reinterpret_cast<float2*>(tile + g * ld + nb * 8 + 2 * t) = make_float2(acc[nb][0], acc[nb][1]);
+        *reinterpret_cast<float2*>(tile + (g + 8) * ld + nb * 8 + 2 * t) = make_float2(acc[nb][2], acc[nb][3]);
+    }
+}
+__device__ __forceinline__ void lc_load(float (&acc)[2][4], const float* tile, int ld) {
+    const int g = (threadIdx.x & 31) >> 2, t = threadIdx.x & 3;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+        const float2 lo = *reinterpret_cast<const float2*>(tile + g * ld + nb * 8 + 2 * t);
+        const float2 hi = *reinterpret_cast<const float2*>(tile + (g + 8) * ld + nb * 8 + 2 * t);
+        acc[nb][0] = lo.x, acc[nb][1] = lo.y, acc[nb][2] = hi.x, acc[nb][3] = hi.y;
+    }
+}
+
 __device__ __forceinline__ void lc_split(float x, bf16& hi, bf16& lo) {
     hi = __float2bfloat16_rn(x);
     lo = __float2bfloat16_rn(x - __bfloat162float(hi));
 }
 
-template <int VB>
+// DC: the head's dim when it is known at compile time (the products' loops over it are then unrolled
+// and their operand loads run ahead of the tensor-core instructions), 0 for any multiple of 16.
+template <int VB, int DC>
 __global__ void __launch_bounds__(LC_WARPS * 32)
 lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, int k_off, int v_off, float* __restrict__ out,
                        long out_stride, float* __restrict__ state, const float* __restrict__ decay,
-                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int H, int D, int V,
-                       int v_blocks) {
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int H, int V,
+                       int D_any, int v_blocks) {
     pdl_trigger();
+    const int D = DC ? DC : D_any;
     extern __shared__ __align__(128) unsigned char lc_smem[];
     const LcSmem L = lc_layout(D, VB);
     bf16* Qs = reinterpret_cast<bf16*>(lc_smem + L.q);
@@ -86,7 +124,8 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
     const int v0 = (blockIdx.x - h * v_blocks) * VB;
     const int t0 = cu_seqlens[seq], nt = cu_seqlens[seq + 1] - t0;
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int DT = D / 16, VT = VB / 16, CT = LC / 16;
+    const int DT = D / 16;
+    constexpr int VT = VB / 16, CT = LC / 16;
     const float w = decay[h];
     for (int p = tid; p <= LC; p += blockDim.x) pw[p] = powf(w, (float)p);
     // the state earlier steps left (zero for a fresh slot): not written by this step's kernels
@@ -160,33 +199,35 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
         if (c0 + LC < nt) fetch(c0 + LC);
 
         // ---- scores q k^T (tiles at or below the diagonal) and q S
-        const int n_a = CT * (CT + 1) / 2, n_o = CT * VT;
+        constexpr int n_a = CT * (CT + 1) / 2, n_o = CT * VT;
         for (int job = warp; job < n_a + n_o; job += LC_WARPS) {
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-            wmma::fill_fragment(acc, 0.0f);
-            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+            float acc[2][4] = {};
+            uint32_t fa[4], fb[4];
             if (job < n_a) {
                 int ti = 0, rest = job;
                 while (rest > ti) rest -= ++ti;              // job -> (ti, tj) with tj <= ti
                 const int tj = rest;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
-                for (int kk = 0; kk < DT; ++kk) {
-                    wmma::load_matrix_sync(a, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
-                    wmma::load_matrix_sync(b, Ks + tj * 16 * L.ldq + kk * 16, L.ldq);
-                    wmma::mma_sync(acc, a, b, acc);
+#pragma unroll
+                for (int kk = 0; kk < (DC ? DC / 16 : DT); ++kk) {
+                    lc_a_rows(fa, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
+                    lc_b_cols(fb, Ks + tj * 16 * L.ldq + kk * 16, L.ldq);      // B[k = d][n = j] = k_j[d]
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
                 }
-                wmma::store_matrix_sync(Af + ti * 16 * L.ldaf + tj * 16, acc, L.ldaf, wmma::mem_row_major);
+                lc_store(Af + ti * 16 * L.ldaf + tj * 16, L.ldaf, acc);
             } else {
                 const int ti = (job - n_a) / VT, tv = (job - n_a) - ti * VT;
-                wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-                for (int kk = 0; kk < DT; ++kk) {
-                    wmma::load_matrix_sync(a, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
-                    wmma::load_matrix_sync(b, Shi + kk * 16 * L.ldv + tv * 16, L.ldv);
-                    wmma::mma_sync(acc, a, b, acc);
-                    wmma::load_matrix_sync(b, Slo + kk * 16 * L.ldv + tv * 16, L.ldv);
-                    wmma::mma_sync(acc, a, b, acc);
+#pragma unroll
+                for (int kk = 0; kk < (DC ? DC / 16 : DT); ++kk) {
+                    lc_a_rows(fa, Qs + ti * 16 * L.ldq + kk * 16, L.ldq);
+                    lc_b_rows(fb, Shi + kk * 16 * L.ldv + tv * 16, L.ldv);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
+                    lc_b_rows(fb, Slo + kk * 16 * L.ldv + tv * 16, L.ldv);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
                 }
-                wmma::store_matrix_sync(Of + ti * 16 * L.ldof + tv * 16, acc, L.ldof, wmma::mem_row_major);
+                lc_store(Of + ti * 16 * L.ldof + tv * 16, L.ldof, acc);
             }
         }
         __syncthreads();
@@ -212,32 +253,37 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
         // ---- o += (decayed scores) v ;  S += k^T (decayed v)
         const int n_s = DT * VT;
         for (int job = warp; job < n_o + n_s; job += LC_WARPS) {
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+            float acc[2][4];
+            uint32_t fa[4], fb[4];
             if (job < n_o) {
                 const int ti = job / VT, tv = job - ti * VT;
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-                wmma::load_matrix_sync(acc, Of + ti * 16 * L.ldof + tv * 16, L.ldof, wmma::mem_row_major);
-                for (int kj = 0; kj <= ti; ++kj) {
-                    wmma::load_matrix_sync(b, Vs + kj * 16 * L.ldv + tv * 16, L.ldv);
-                    wmma::load_matrix_sync(a, Ahi + ti * 16 * L.lda + kj * 16, L.lda);
-                    wmma::mma_sync(acc, a, b, acc);
-                    wmma::load_matrix_sync(a, Alo + ti * 16 * L.lda + kj * 16, L.lda);
-                    wmma::mma_sync(acc, a, b, acc);
+                lc_load(acc, Of + ti * 16 * L.ldof + tv * 16, L.ldof);
+#pragma unroll
+                for (int kj = 0; kj < CT; ++kj) {
+                    if (kj > ti) break;
+                    lc_b_rows(fb, Vs + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    lc_a_rows(fa, Ahi + ti * 16 * L.lda + kj * 16, L.lda);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
+                    lc_a_rows(fa, Alo + ti * 16 * L.lda + kj * 16, L.lda);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
                 }
-                wmma::store_matrix_sync(Of + ti * 16 * L.ldof + tv * 16, acc, L.ldof, wmma::mem_row_major);
+                lc_store(Of + ti * 16 * L.ldof + tv * 16, L.ldof, acc);
             } else {
                 const int td = (job - n_o) / VT, tv = (job - n_o) - td * VT;
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::col_major> a;      // k^T: [d][j] = Ks[j][d]
-                wmma::load_matrix_sync(acc, Sf + td * 16 * L.ldsf + tv * 16, L.ldsf, wmma::mem_row_major);
+                lc_load(acc, Sf + td * 16 * L.ldsf + tv * 16, L.ldsf);
+#pragma unroll
                 for (int kj = 0; kj < CT; ++kj) {
-                    wmma::load_matrix_sync(a, Ks + kj * 16 * L.ldq + td * 16, L.ldq);
-                    wmma::load_matrix_sync(b, Vhi + kj * 16 * L.ldv + tv * 16, L.ldv);
-                    wmma::mma_sync(acc, a, b, acc);
-                    wmma::load_matrix_sync(b, Vlo + kj * 16 * L.ldv + tv * 16, L.ldv);
-                    wmma::mma_sync(acc, a, b, acc);
+                    lc_a_cols(fa, Ks + kj * 16 * L.ldq + td * 16, L.ldq);        // A[m = d][k = j] = k_j[d]
+                    lc_b_rows(fb, Vhi + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
+                    lc_b_rows(fb, Vlo + kj * 16 * L.ldv + tv * 16, L.ldv);
+                    mma16816(acc[0], fa, fb[0], fb[1]);
+                    mma16816(acc[1], fa, fb[2], fb[3]);
                 }
-                wmma::store_matrix_sync(Sf + td * 16 * L.ldsf + tv * 16, acc, L.ldsf, wmma::mem_row_major);
+                lc_store(Sf + td * 16 * L.ldsf + tv * 16, L.ldsf, acc);
             }
         }
         __syncthreads();
@@ -259,17 +305,17 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
     }
 }
 
-template <int VB>
+template <int VB, int DC>
 static int launch_chunks(const bf16* proj, long stride, int q_off, int k_off, int v_off, float* out, long out_stride,
                          float* state, const float* decay, const int* cu_seqlens, const int* seq_slot, int n_seqs, int H,
                          int D, int V, cudaStream_t stream) {
     const LcSmem L = lc_layout(D, VB);
     const int v_blocks = (V + VB - 1) / VB;
-    auto kernel = lightning_chunk_kernel<VB>;
+    auto kernel = lightning_chunk_kernel<VB, DC>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total);
     if (e != cudaSuccess) return bfi_fail("lightning_chunks: cannot reserve %zu bytes of shared memory: %s", L.total, cudaGetErrorString(e));
     bfi_launch(kernel, dim3(H * v_blocks, n_seqs), dim3(LC_WARPS * 32), L.total, stream, proj, stride, q_off, k_off, v_off, out,
-               out_stride, state, decay, cu_seqlens, seq_slot, H, D, V, v_blocks);
+               out_stride, state, decay, cu_seqlens, seq_slot, H, V, D, v_blocks);
     return bfi_check_launch("lightning_chunks");
 }
 
@@ -295,9 +341,17 @@ extern "C" int bfi_lightning_chunks_bf16(const void* proj, long stride, int q_of
     }
     if (vb == 0) return 2;
     const bf16* p = (const bf16*)proj;
-    if (vb == 64) return launch_chunks<64>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
-    if (vb == 32) return launch_chunks<32>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
-    return launch_chunks<16>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream);
+#define BFI_LC(VBB, DCC) \
+    return launch_chunks<VBB, DCC>(p, stride, q_off, k_off, v_off, out, out_stride, state, decay, cu_seqlens, seq_slot, n_seqs, H, D, V, stream)
+#define BFI_LC_D(VBB)          \
+    if (D == 128) BFI_LC(VBB, 128); \
+    if (D == 64) BFI_LC(VBB, 64);   \
+    BFI_LC(VBB, 0)
+    if (vb == 64) { BFI_LC_D(64); }
+    if (vb == 32) { BFI_LC_D(32); }
+    BFI_LC_D(16);
+#undef BFI_LC_D
+#undef BFI_LC
 }
 
 BFI_TRACE_EXPORT(lightning_chunked)
