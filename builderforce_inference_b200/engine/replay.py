@@ -29,8 +29,11 @@ def add_arguments(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
+
+
+REPLAY_SLOTS = 64          # requests the replay's cache is first sized for (it grows past them on demand)
 
 
 def replay(args, lines=None) -> int:
@@ -40,7 +43,11 @@ def replay(args, lines=None) -> int:
     from .engine import Engine, SequenceStep
 
     os.makedirs(args.out, exist_ok=True)
-    engine = Engine.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device)
+    # --max-tokens counts the tokens themselves; a request's last page is rarely full, so the cache gets
+    # one page of slack for each of the requests it can hold side by side
+    from ..cache.pages import PAGE_TOKENS
+    engine = Engine.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens + REPLAY_SLOTS * PAGE_TOKENS,
+                         device=args.device, cache_slots=REPLAY_SLOTS)
     slots = {}
     for line in (sys.stdin if lines is None else lines):
         line = line.strip()

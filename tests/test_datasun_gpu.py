@@ -316,7 +316,7 @@ def test_prepare_kernel_bias_row_norm_adjacent_rotation_values_from_keys(dt, n_q
 
 def test_rotation_table_with_scaled_frequencies():
     from builderforce_inference_b200.parts.rotary import rotary_table
-    for base, dims, sc in ((1e6, 16, yarn(2.0, 512, 32.0, 1.0)), (5000.0, 12, yarn(4.0, 64, 16.0, 2.0)), (100.0, 8, None),
+    for base, dims, sc in ((3e5, 24, yarn(3.0, 256, 24.0, 1.5)), (5000.0, 12, yarn(4.0, 64, 16.0, 2.0)), (100.0, 8, None),
                            (1e4, 64, yarn(8.0, 4096, 32.0, 1.0))):
         f, mag = P.rotary_frequencies(base, dims, sc)
         ang = torch.arange(300, dtype=torch.float64)[:, None] * f[None]
