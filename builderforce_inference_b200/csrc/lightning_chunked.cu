@@ -11,13 +11,13 @@
 // into a bfloat16 head and a bfloat16 remainder and the product is taken with both, which keeps
 // 16 bits of mantissa; the master copy of the state stays float32 and is only ever added to.
 //
-// A block owns VB columns of one head of one sequence and walks the sequence's chunks in order;
+// A block (16 warps) owns VB columns of one head of one sequence and walks the sequence's chunks in order;
 // the matrix products are 16x16 tiles of mma.sync.m16n8k16 (operands by ldmatrix) dealt round-robin to
-// its 8 warps.
+// its warps.
 #include "attention_tiles.cuh"
 
 #define LC 64          // tokens per chunk
-#define LC_WARPS 8      // (AD_WARPS of attention_tiles.cuh belongs to the attention kernels)
+#define LC_WARPS 16     // (AD_WARPS of attention_tiles.cuh belongs to the attention kernels)
 
 __device__ __forceinline__ float lc_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -143,7 +143,7 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
     // when their turn comes, so the trip to memory hides behind a chunk's products.
     const int D8 = D >> 3;
     constexpr int VB8 = VB / 8;
-    constexpr int NQ = 4, NV = (LC * VB8 + LC_WARPS * 32 - 1) / (LC_WARPS * 32);
+    constexpr int NQ = LC * 16 / (LC_WARPS * 32), NV = (LC * VB8 + LC_WARPS * 32 - 1) / (LC_WARPS * 32);
     uint4 rq[NQ], rk[NQ], rv[NV];
     auto fetch = [&](int c0) {
         const int n = min(LC, nt - c0);
@@ -191,11 +191,11 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
         }
     };
     fetch(0);
+    stash();
+    __syncthreads();
 
     for (int c0 = 0; c0 < nt; c0 += LC) {
         const int n = min(LC, nt - c0);
-        stash();
-        __syncthreads();
         if (c0 + LC < nt) fetch(c0 + LC);
 
         // ---- scores q k^T (tiles at or below the diagonal) and q S
@@ -297,6 +297,8 @@ lightning_chunk_kernel(const bf16* __restrict__ proj, long stride, int q_off, in
             const int d = i / VB, c = i - d * VB;
             lc_split(Sf[d * L.ldsf + c], Shi[d * L.ldv + c], Slo[d * L.ldv + c]);
         }
+        // ... and, in the same phase, the next chunk's q, k, v (the products that read this chunk's are done)
+        if (c0 + LC < nt) stash();
         __syncthreads();
     }
     for (int i = tid; i < D * VB; i += blockDim.x) {
@@ -329,15 +331,20 @@ extern "C" int bfi_lightning_chunks_bf16(const void* proj, long stride, int q_of
     if (D % 16 != 0 || D > 128 || V % 16 != 0 || n_seqs > 65535) return 2;
     // q, k and v are read in 16-byte pieces
     if (((uintptr_t)proj & 15) != 0 || stride % 8 != 0 || q_off % 8 != 0 || k_off % 8 != 0 || v_off % 8 != 0) return 2;
-    // columns per block: as many as fit shared memory, fewer when that is needed to fill the GPU
+    // Columns per block.  A chunk costs a block a fixed part (its phases' barriers and latencies) and a
+    // part per column, measured at 9.2, 6.3 and 4.7 us for 64, 32 and 16 columns; a launch takes as many
+    // rounds as its blocks need on the GPU's SMs (one block per SM).  The cheapest product wins.
     const size_t limit = 200 * 1024;
+    const int n_sm = bfi_sm_count();
     int vb = 0;
-    for (int cand : {64, 32, 16}) {
-        if (V % cand != 0 && cand != 16) continue;
-        if (lc_layout(D, cand).total > limit) continue;
-        if (vb == 0) vb = cand;
-        if ((long)n_seqs * H * ((V + vb - 1) / vb) >= bfi_sm_count()) break;
-        vb = cand;
+    double best = 0.0;
+    for (int c = 0; c < 3; ++c) {
+        const int cand = 64 >> c;
+        const double per_chunk = c == 0 ? 9.2 : (c == 1 ? 6.3 : 4.7);
+        if (V % cand != 0 || lc_layout(D, cand).total > limit) continue;
+        const long blocks = (long)n_seqs * H * (V / cand);
+        const double cost = (double)((blocks + n_sm - 1) / n_sm) * per_chunk;
+        if (vb == 0 || cost < best) vb = cand, best = cost;
     }
     if (vb == 0) return 2;
     const bf16* p = (const bf16*)proj;
