@@ -33,12 +33,23 @@ class KVView:
     """What an attention kernel needs to reach one run's keys and values."""
 
     k: torch.Tensor            # [pages, kv_heads, PAGE_TOKENS, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor            # [pages, kv_heads, PAGE_TOKENS, v_dim]
     block_table: torch.Tensor  # [slots, blocks] int32 on the device
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
     page_tokens: int = PAGE_TOKENS
+    v_dim: Optional[int] = None        # None: as head_dim
+    chunk: Optional[int] = None        # a token reads only its own block of `chunk` positions
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
+
+    @property
+    def plain(self) -> bool:
+        """Keys and values of one size and no chunked mask: what every attention kernel takes."""
+        return self.value_dim == self.head_dim and self.chunk is None
 
 
 @dataclass
@@ -70,12 +81,19 @@ class _KVGroup:
         self.need = need
         self.keys = keys                       # (run, index among the run's needs) per place
         self.runs = [r for r, _ in keys]
-        self.table = PageTable(n_pages, need.window)
+        self.table = PageTable(n_pages, need.window, need.chunk)
         self.n_blocks = n_blocks
         self.device = device
-        self.storage = torch.empty(
-            (len(keys), 2, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
-            dtype=dtype, device=device)
+        self.storage = self.v_storage = None
+        if need.value_dim == need.head_dim:
+            self.storage = torch.empty(
+                (len(keys), 2, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
+                dtype=dtype, device=device)
+        else:       # values of another size than the keys: a tensor each
+            self.storage = torch.empty((len(keys), 1, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
+                                       dtype=dtype, device=device)
+            self.v_storage = torch.empty((len(keys), n_pages, need.n_kv_heads, PAGE_TOKENS, need.value_dim),
+                                         dtype=dtype, device=device)
         self._alloc_tables(n_slots)
 
     def _alloc_tables(self, n_slots: int) -> None:
@@ -102,12 +120,18 @@ class _KVGroup:
 
     def view(self, key) -> KVView:
         i = self.keys.index(key)
-        return KVView(k=self.storage[i, 0], v=self.storage[i, 1], block_table=self.block_dev,
+        v = self.storage[i, 1] if self.v_storage is None else self.v_storage[i]
+        return KVView(k=self.storage[i, 0], v=v, block_table=self.block_dev,
                       n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
-                      window=self.need.window)
+                      window=self.need.window, v_dim=self.need.v_dim, chunk=self.need.chunk)
 
     def bytes_per_token(self) -> int:
-        return len(self.runs) * 2 * self.need.n_kv_heads * self.need.head_dim * self.storage.element_size()
+        return len(self.runs) * self.need.n_kv_heads * (self.need.head_dim + self.need.value_dim) * self.storage.element_size()
+
+    def fill(self, value: float) -> None:
+        self.storage.fill_(value)
+        if self.v_storage is not None:
+            self.v_storage.fill_(value)
 
 
 class _StateGroup:
@@ -267,7 +291,7 @@ class SequenceCache:
         for s, c in zip(slots, counts):
             self.lengths[s] += c
         for g in self.kv_groups:
-            if g.need.window is None:
+            if g.table.keeps_everything:
                 continue
             for s in slots:
                 if g.table.trim(s, self.lengths[s]):
@@ -292,6 +316,10 @@ class SequenceCache:
         if windowed:
             raise CacheError(f"rewind unsupported: layers with a window of {windowed[0]} keys have given "
                              "back pages the shorter sequence would read; release the slot and start again")
+        chunked = [g.need.chunk for g in self.kv_groups if g.need.chunk is not None]
+        if chunked:
+            raise CacheError(f"rewind unsupported: layers that read chunks of {chunked[0]} keys have given "
+                             "back pages the shorter sequence would read; release the slot and start again")
         for g in self.kv_groups:
             if g.table.shrink(slot, length):
                 g.sync_row(slot)
@@ -309,7 +337,7 @@ class SequenceCache:
         total = 0
         for g in self.kv_groups:
             for s, n in self.lengths.items():
-                kept = n - g.table.first_kept_position(n) if g.need.window is not None else n
+                kept = n - g.table.first_kept_position(n)
                 total += kept * g.bytes_per_token()
         return total
 
@@ -323,4 +351,4 @@ class SequenceCache:
     def poison(self, value: float = float("nan")) -> None:
         """Fill every page with ``value`` (tests: rows past a sequence's length must never matter)."""
         for g in self.kv_groups:
-            g.storage.fill_(value)
+            g.fill(value)

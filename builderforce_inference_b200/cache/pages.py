@@ -74,14 +74,16 @@ class FreeList:
 class PageTable:
     """For one group of layers: per slot, which page holds positions ``64*i .. 64*i+63``.
 
-    ``window`` is None when every earlier position is kept.  Otherwise only pages that still
-    hold a position inside the window of the sequence's next token are kept; ``trim`` gives the
+    ``window`` and ``chunk`` are None when every earlier position is kept.  Otherwise only pages
+    that still hold a position the sequence's next token may read are kept (the last ``window``
+    positions; the positions of the token's own block of ``chunk`` positions); ``trim`` gives the
     others back.
     """
 
-    def __init__(self, n_pages: int, window: Optional[int] = None):
+    def __init__(self, n_pages: int, window: Optional[int] = None, chunk: Optional[int] = None):
         self.pool = FreeList(n_pages, "page")
         self.window = window
+        self.chunk = chunk
         self.rows: Dict[int, List[int]] = {}      # slot -> page id per position block (-1: none)
 
     def open(self, slot: int) -> None:
@@ -91,9 +93,16 @@ class PageTable:
 
     def first_kept_position(self, length: int) -> int:
         """The oldest position the next token (at ``length``) may still read."""
-        if self.window is None:
-            return 0
-        return max(0, length - self.window + 1)
+        first = 0
+        if self.window is not None:
+            first = max(first, length - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, length // self.chunk * self.chunk)
+        return first
+
+    @property
+    def keeps_everything(self) -> bool:
+        return self.window is None and self.chunk is None
 
     def pages_needed(self, slot: int, start: int, end: int) -> int:
         """How many new pages ``ensure(slot, start, end)`` would take."""
@@ -116,8 +125,8 @@ class PageTable:
         return changed
 
     def trim(self, slot: int, length: int) -> bool:
-        """Give back pages that lie wholly before the window of the token at ``length``."""
-        if self.window is None:
+        """Give back pages that lie wholly before what the token at ``length`` may read."""
+        if self.keeps_everything:
             return False
         row = self.rows[slot]
         first_block = self.first_kept_position(length) // PAGE_TOKENS

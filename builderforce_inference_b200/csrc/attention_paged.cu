@@ -6,8 +6,12 @@
 // Reference formula (crates/bfi-core/src/cpu.rs:328-392): score = q.k / sqrt(d) for keys at or
 // before the query's position, softmax over them, weighted sum of V; query head h reads kv head
 // h / (n_q / n_kv).  `window` > 0 keeps only the last `window` keys (pos - window < j <= pos).
+// `chunk` > 0 keeps only the keys of the query's own block of `chunk` consecutive positions, blocks
+// counted from position 0 of the sequence ((pos / chunk) * chunk <= j <= pos).
 // `has_sink`: the softmax's denominator carries one more term, exp(sink), a score that every
-// query sees and that has no value: p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)).
+// query sees and that has no value: p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); the sink is one
+// number (`has_sink` 1) or one float32 per query head (`has_sink` 2, `sinks`).
+// Keys have `d` values per head, values `dv` (the cache's value pages are laid out by `dv`).
 //
 // Work split: one block per (sequence, kv head, chunk of heads of its group, chunk of tokens);
 // 16 query rows per block (GH heads x 16/GH consecutive tokens) share each tile of 32 keys that
@@ -27,13 +31,14 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv, int d,
-                       int gh, int head_chunks, int window, float scale, int has_sink, float sink) {
+                       int dv, int gh, int head_chunks, int window, int chunk, float scale, int has_sink, float sink,
+                       const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                          // [ATT_ROWS][d]
     float* ks = qs + ATT_ROWS * d;             // [ATT_KEYS][d + 1]
-    float* vs = ks + ATT_KEYS * (d + 1);       // [ATT_KEYS][d]
+    float* vs = ks + ATT_KEYS * (d + 1);       // [ATT_KEYS][dv]
 
     const int seq = blockIdx.z;
     const int slot = seq_slot[seq];
@@ -72,6 +77,7 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
         row_ok[i] = tok < nt && hl < group;
         row_pos[i] = start + tok;
         row_lo[i] = window > 0 ? max(0, row_pos[i] - window + 1) : 0;
+        if (chunk > 0) row_lo[i] = max(row_lo[i], (row_pos[i] / chunk) * chunk);
     }
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.0f, 0.0f};
@@ -84,24 +90,31 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
     // ---- key range of the block
     const int last_tok = min(tok0 + qt, nt) - 1;
     const int hi = start + last_tok;                                     // last key any row reads
-    const int lo = window > 0 ? max(0, start + tok0 - window + 1) : 0;   // first key any row reads
+    int lo = window > 0 ? max(0, start + tok0 - window + 1) : 0;         // first key any row reads
+    if (chunk > 0) lo = max(lo, ((start + tok0) / chunk) * chunk);
     const size_t page_elems = (size_t)n_kv * BFI_PAGE_TOKENS * d;
+    const size_t page_elems_v = (size_t)n_kv * BFI_PAGE_TOKENS * dv;
 
     for (int kb = (lo / ATT_KEYS) * ATT_KEYS; kb <= hi; kb += ATT_KEYS) {
         __syncthreads();
         const int page = block_table[(size_t)slot * table_stride + kb / BFI_PAGE_TOKENS];
         const size_t base = (size_t)(page < 0 ? 0 : page) * page_elems +
                             ((size_t)kvh * BFI_PAGE_TOKENS + (kb % BFI_PAGE_TOKENS)) * d;
+        const size_t base_v = (size_t)(page < 0 ? 0 : page) * page_elems_v +
+                              ((size_t)kvh * BFI_PAGE_TOKENS + (kb % BFI_PAGE_TOKENS)) * dv;
         for (int i = threadIdx.x; i < ATT_KEYS * d; i += blockDim.x) {
             const int j = i / d, e = i - j * d;
             const int key = kb + j;
-            float kv = 0.0f, vv = 0.0f;
-            if (page >= 0 && key >= lo && key <= hi) {
-                kv = to_f32(k_pages[base + (size_t)j * d + e]);
-                vv = to_f32(v_pages[base + (size_t)j * d + e]);
-            }
+            float kv = 0.0f;
+            if (page >= 0 && key >= lo && key <= hi) kv = to_f32(k_pages[base + (size_t)j * d + e]);
             ks[j * (d + 1) + e] = kv;
-            vs[j * d + e] = vv;
+        }
+        for (int i = threadIdx.x; i < ATT_KEYS * dv; i += blockDim.x) {
+            const int j = i / dv, e = i - j * dv;
+            const int key = kb + j;
+            float vv = 0.0f;
+            if (page >= 0 && key >= lo && key <= hi) vv = to_f32(v_pages[base_v + (size_t)j * dv + e]);
+            vs[j * dv + e] = vv;
         }
         __syncthreads();
 
@@ -131,11 +144,11 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
             for (int jj = 0; jj < ATT_KEYS; ++jj) {
                 const float pj = __shfl_sync(0xffffffffu, p, jj);
                 if (pj == 0.0f) continue;
-                const float* vr = vs + jj * d;
+                const float* vr = vs + jj * dv;
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int e = lane + 32 * c;
-                    if (e < d) acc[i][c] = fmaf(pj, vr[e], acc[i][c]);
+                    if (e < dv) acc[i][c] = fmaf(pj, vr[e], acc[i][c]);
                 }
             }
         }
@@ -148,13 +161,14 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
         const int tok = tok0 + r / gh;
         const int hl = hc * gh + r % gh;
         float l = l_run[i];
-        if (has_sink && m_run[i] > -INFINITY) l += expf(sink - m_run[i]);
+        const float sk = has_sink == 2 ? sinks[kvh * group + hl] : sink;
+        if (has_sink && m_run[i] > -INFINITY) l += expf(sk - m_run[i]);
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        T* o = out + (size_t)(t0 + tok) * out_stride + (size_t)(kvh * group + hl) * d;
+        T* o = out + (size_t)(t0 + tok) * out_stride + (size_t)(kvh * group + hl) * dv;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
             const int e = lane + 32 * c;
-            if (e < d) o[e] = from_f32<T>(acc[i][c] * inv);
+            if (e < dv) o[e] = from_f32<T>(acc[i][c] * inv);
         }
     }
 }
@@ -163,7 +177,8 @@ template <typename T, int NC>
 static int launch_attention(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                             const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                             const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv,
-                            int d, int window, float scale, int has_sink, float sink, cudaStream_t stream) {
+                            int d, int dv, int window, int chunk, float scale, int has_sink, float sink,
+                            const float* sinks, cudaStream_t stream) {
     const int group = n_q / n_kv;
     int gh = 1;
     while (gh < group && gh < 8) gh *= 2;
@@ -172,7 +187,7 @@ static int launch_attention(const void* q, long q_stride, void* out, long out_st
     dim3 grid((max_tokens + qt - 1) / qt, n_kv * head_chunks, n_seqs);
     BFI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "attention_paged: too many heads (%d) or sequences (%d) for one launch",
                 (int)grid.y, n_seqs);
-    const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + ATT_KEYS * d) * sizeof(float);
+    const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + ATT_KEYS * dv) * sizeof(float);
     auto kernel = attention_paged_kernel<T, NC>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -181,7 +196,7 @@ static int launch_attention(const void* q, long q_stride, void* out, long out_st
     }
     bfi_launch(kernel, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,
                                                    (const T*)v_pages, block_table, table_stride, cu_seqlens, seq_slot,
-                                                   seq_start, n_q, n_kv, d, gh, head_chunks, window, scale, has_sink, sink);
+                                                   seq_start, n_q, n_kv, d, dv, gh, head_chunks, window, chunk, scale, has_sink, sink, sinks);
     return bfi_check_launch("attention_paged");
 }
 
@@ -189,12 +204,13 @@ template <typename T>
 static int dispatch_nc(int nc, const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                        const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                        const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv, int d,
-                       int window, float scale, int has_sink, float sink, cudaStream_t stream) {
+                       int dv, int window, int chunk, float scale, int has_sink, float sink, const float* sinks,
+                       cudaStream_t stream) {
 #define BFI_ATT_CASE(N)                                                                                              \
     case N:                                                                                                          \
         return launch_attention<T, N>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,     \
-                                      cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window,     \
-                                      scale, has_sink, sink, stream);
+                                      cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, dv, window, \
+                                      chunk, scale, has_sink, sink, sinks, stream);
     switch (nc) {
         BFI_ATT_CASE(1)
         BFI_ATT_CASE(2)
@@ -213,24 +229,26 @@ static int dispatch_nc(int nc, const void* q, long q_stride, void* out, long out
 extern "C" int bfi_attention_paged(const void* q, int dtype, long q_stride, void* out, long out_stride,
                                    const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                                    const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
-                                   int max_tokens, int n_q, int n_kv, int d, int window, float scale, int has_sink,
-                                   float sink, cudaStream_t stream) {
+                                   int max_tokens, int n_q, int n_kv, int d, int dv, int window, int chunk, float scale,
+                                   int has_sink, float sink, const float* sinks, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "attention_paged: unknown dtype code %d", dtype);
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_paged: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(d > 0 && d % 2 == 0 && d <= ATT_MAX_D, "attention_paged: head_dim %d must be even, at most %d",
                 d, ATT_MAX_D);
-    BFI_REQUIRE(window >= 0, "attention_paged: negative window");
-    BFI_REQUIRE(q_stride >= (long)n_q * d && out_stride >= (long)n_q * d, "attention_paged: token stride shorter than the heads");
+    BFI_REQUIRE(dv > 0 && dv <= ATT_MAX_D, "attention_paged: value size %d must be positive, at most %d", dv, ATT_MAX_D);
+    BFI_REQUIRE(window >= 0 && chunk >= 0, "attention_paged: negative window or chunk");
+    BFI_REQUIRE(has_sink != 2 || sinks != nullptr, "attention_paged: a sink per head needs its array");
+    BFI_REQUIRE(q_stride >= (long)n_q * d && out_stride >= (long)n_q * dv, "attention_paged: token stride shorter than the heads");
     if (n_seqs <= 0 || max_tokens <= 0) return 0;
     // round the slice count up to an instantiated value
-    int nc = (d + 31) / 32;
+    int nc = (dv + 31) / 32;
     if (nc == 5) nc = 6;
     if (nc == 7) nc = 8;
     if (nc > 8) nc = 16;
     if (dtype == BFI_F32)
         return dispatch_nc<float>(nc, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
-                                  cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, has_sink, sink, stream);
+                                  cu_seqlens, seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, dv, window, chunk, scale, has_sink, sink, sinks, stream);
     return dispatch_nc<bf16>(nc, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                             seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, window, scale, has_sink, sink, stream);
+                             seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, d, dv, window, chunk, scale, has_sink, sink, sinks, stream);
 }

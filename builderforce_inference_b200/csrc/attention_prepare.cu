@@ -17,6 +17,8 @@
 //   6. the output projection's bias, added to the token's row of the float32 residual stream:
 //                 nothing reads that row between the block's norm and the output projection,
 //                 which accumulates into it
+// A value head has `dv` values, which need not be the keys' `d` (the row is q heads, k heads, then v
+// heads of dv values each; the cache's value pages are laid out by dv).
 // All arithmetic is float32; storage is float32 or bfloat16.
 #include "common.cuh"
 
@@ -32,7 +34,7 @@
 
 struct PrepArgs {
     long token_stride;
-    int n_tokens, n_q, n_kv, d;
+    int n_tokens, n_q, n_kv, d, dv;
     const void *q_bias, *k_bias, *v_bias;
     int bias_dtype;
     const void *q_norm_w, *k_norm_w;
@@ -97,8 +99,9 @@ __global__ void __launch_bounds__(PREP_THREADS) qk_prepare_kernel(T* __restrict_
         } else {
             // ---- 2. the values: the keys as they stand now, or the row's own v heads
             T* vp = reinterpret_cast<T*>(a.v_pages);
-            for (int j = threadIdx.x; j < nk; j += PREP_THREADS) {
-                const int h = j / d, e = j - h * d;
+            const int dv = own_v ? a.dv : d;     // values that are the keys have the keys' size
+            for (int j = threadIdx.x; j < a.n_kv * dv; j += PREP_THREADS) {
+                const int h = j / dv, e = j - h * dv;
                 float v;
                 if (own_v) {
                     v = to_f32(row[nq + nk + j]);
@@ -106,7 +109,7 @@ __global__ void __launch_bounds__(PREP_THREADS) qk_prepare_kernel(T* __restrict_
                 } else {
                     v = rowbuf[nq + j];
                 }
-                vp[(((size_t)page * a.n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * d + e] = from_f32<T>(v);
+                vp[(((size_t)page * a.n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * dv + e] = from_f32<T>(v);
             }
         }
     }
@@ -166,7 +169,7 @@ __global__ void __launch_bounds__(PREP_THREADS) qk_prepare_kernel(T* __restrict_
     }
 }
 
-extern "C" int bfi_qk_prepare(void* qkv, int dtype, long token_stride, int n_tokens, int n_q, int n_kv, int d,
+extern "C" int bfi_qk_prepare(void* qkv, int dtype, long token_stride, int n_tokens, int n_q, int n_kv, int d, int dv,
                               const void* q_bias, const void* k_bias, const void* v_bias, int bias_dtype,
                               const void* q_norm_w, const void* k_norm_w, int norm_dtype, int norm_mode, float eps,
                               const void* rope_table, int rot_dim, int table_positions, int pairing,
@@ -181,7 +184,8 @@ extern "C" int bfi_qk_prepare(void* qkv, int dtype, long token_stride, int n_tok
     BFI_REQUIRE(norm_mode >= PREP_NORM_NONE && norm_mode <= PREP_NORM_ROW, "qk_prepare: unknown norm mode %d", norm_mode);
     BFI_REQUIRE(pairing == PREP_PAIR_HALF || pairing == PREP_PAIR_ADJACENT, "qk_prepare: unknown pairing %d", pairing);
     const bool own_v = !(flags & PREP_VALUES_ARE_KEYS);
-    BFI_REQUIRE(token_stride >= (long)(n_q + (own_v ? 2 : 1) * n_kv) * d, "qk_prepare: token stride shorter than the heads");
+    BFI_REQUIRE(dv > 0 && (own_v || dv == d), "qk_prepare: value size %d (values that are the keys have the keys' size %d)", dv, d);
+    BFI_REQUIRE(token_stride >= (long)(n_q + n_kv) * d + (own_v ? (long)n_kv * dv : 0), "qk_prepare: token stride shorter than the heads");
     if (rope_table) {
         BFI_REQUIRE(rot_dim > 0 && rot_dim % 2 == 0 && rot_dim <= d,
                     "qk_prepare: rotary width %d must be even and at most head_dim %d", rot_dim, d);
@@ -194,7 +198,7 @@ extern "C" int bfi_qk_prepare(void* qkv, int dtype, long token_stride, int n_tok
     const size_t smem = (size_t)(n_q + n_kv) * d * sizeof(float);
     BFI_REQUIRE(smem <= 200 * 1024, "qk_prepare: %d values of q and k per token do not fit shared memory", (n_q + n_kv) * d);
     PrepArgs a;
-    a.token_stride = token_stride, a.n_tokens = n_tokens, a.n_q = n_q, a.n_kv = n_kv, a.d = d;
+    a.token_stride = token_stride, a.n_tokens = n_tokens, a.n_q = n_q, a.n_kv = n_kv, a.d = d, a.dv = dv;
     a.q_bias = q_bias, a.k_bias = k_bias, a.v_bias = v_bias, a.bias_dtype = bias_dtype;
     a.q_norm_w = q_norm_w, a.k_norm_w = k_norm_w, a.norm_dtype = norm_dtype, a.norm_mode = norm_mode, a.eps = eps;
     a.rope_table = (const float2*)rope_table, a.rot_dim = rot_dim, a.table_positions = table_positions, a.pairing = pairing;

@@ -1,0 +1,306 @@
+// Linear recurrences with a decay that depends on the token, and what stands around them: the
+// general kernels (any sizes, any step shape: whole prompts, further pieces, single tokens),
+// float32 or bfloat16 storage of the inputs, float32 arithmetic and float32 state.
+//
+// Per sequence and head, with q_t, k_t (D values) and v_t (V values):
+//     S_t = diag(a_t) S_(t-1) + k_t (c_t v_t)^T          S is D x V, float32, kept per slot
+//     o_t = S_t^T q_t + skip * v_t
+// The decay a_t and the factor c_t come from a raw value r of the token (a projection's output)
+// in one of these forms, all evaluated here in float32:
+//     REC_DECAY_STEP      one r per head:   c = softplus(r + bias_h), a = exp(-rate_h * c) for all rows
+//                         (a discretised state space: c is the step size, rate_h > 0)
+//     REC_DECAY_SIGMOID   one r per row d:  a_d = sigmoid(r + bias_(h,d))^(1/tau), c = 1
+// Heads may share q and k in groups (q_t and k_t of head h are those of group h / heads_per_group).
+// Column j of S, and with it value j of o, depends on no other column, so a block owns a range of
+// columns of one head of one sequence and walks the sequence's new tokens in order.
+//
+// bfi_causal_conv: a short causal convolution per channel over the step's tokens with silu, whose
+// last taps-1 inputs per sequence are kept as state (zero before the first token).
+// bfi_gated_group_norm: the gate and the norm in equal parts that follow such a recurrence.
+#include "common.cuh"
+
+#define REC_DECAY_STEP 1
+#define REC_DECAY_SIGMOID 2
+#define REC_MAX_TAPS 16
+
+__device__ __forceinline__ float rec_sigmoid(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+    const float z = expf(x);
+    return z / (1.0f + z);
+}
+__device__ __forceinline__ float rec_silu(float x) { return x * rec_sigmoid(x); }
+__device__ __forceinline__ float rec_softplus(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float rec_log_sigmoid(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
+
+struct RecArgs {
+    long qk_stride, v_stride, r_stride, out_stride;   // elements between tokens
+    int q_off, k_off, v_off, r_off;                    // first column of each in its row
+    int H, D, V, heads_per_group;
+    int mode;
+    float q_scale, inv_tau;
+    const float *bias, *rate, *skip;                   // float32: [H] or [H*D] bias, [H] rate, [H] skip (or null)
+    const int *cu_seqlens, *seq_slot;
+    int vb, v_blocks;
+};
+
+template <typename T>
+__global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, const T* __restrict__ raw,
+                                  float* __restrict__ out, float* __restrict__ state, const RecArgs a) {
+    pdl_trigger();
+    extern __shared__ float sm[];
+    const int D = a.D, V = a.V, vb = a.vb;
+    float* S = sm;                      // [D][vb]
+    float* qs = S + (size_t)D * vb;     // [D]
+    float* ks = qs + D;                 // [D]
+    float* as = ks + D;                 // [D] decay per row
+    float* red = as + D;                // [threads]
+    __shared__ float step_c;
+    const int seq = blockIdx.y;
+    const int slot = a.seq_slot[seq];
+    if (slot < 0) return;
+    const int h = blockIdx.x / a.v_blocks;
+    const int v0 = (blockIdx.x - h * a.v_blocks) * vb;
+    const int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
+    const int c = threadIdx.x % vb, g = threadIdx.x / vb, ng = blockDim.x / vb;
+    const bool col_ok = v0 + c < V;
+    const int grp = h / a.heads_per_group;
+    const float skip = a.skip ? a.skip[h] : 0.0f;
+    // the state of earlier steps (zeroed when the slot was taken) does not come from this step's kernels
+    float* sp = state + (((size_t)slot * a.H + h) * D) * V + v0;
+    for (int d = g; d < D; d += ng) S[d * vb + c] = col_ok ? sp[(size_t)d * V + c] : 0.0f;
+    pdl_wait();
+    for (int t = 0; t < nt; ++t) {
+        const size_t tok = (size_t)(t0 + t);
+        const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
+        const T* rr = raw + tok * a.r_stride + a.r_off;
+        if (a.mode == REC_DECAY_STEP) {
+            if (threadIdx.x == 0) step_c = rec_softplus(to_f32(rr[h]) + a.bias[h]);
+            __syncthreads();
+            const float w = expf(-a.rate[h] * step_c);
+            for (int j = threadIdx.x; j < D; j += blockDim.x) {
+                qs[j] = to_f32(row[a.q_off + j]) * a.q_scale;
+                ks[j] = to_f32(row[a.k_off + j]);
+                as[j] = w;
+            }
+        } else {
+            if (threadIdx.x == 0) step_c = 1.0f;
+            for (int j = threadIdx.x; j < D; j += blockDim.x) {
+                qs[j] = to_f32(row[a.q_off + j]) * a.q_scale;
+                ks[j] = to_f32(row[a.k_off + j]);
+                as[j] = expf(rec_log_sigmoid(to_f32(rr[(size_t)h * D + j]) + a.bias[(size_t)h * D + j]) * a.inv_tau);
+            }
+        }
+        float vv = 0.0f;
+        if (col_ok) vv = to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + v0 + c]);
+        __syncthreads();
+        const float cv = step_c * vv;
+        float acc = 0.0f;
+        for (int d = g; d < D; d += ng) {
+            const float s = fmaf(as[d], S[d * vb + c], ks[d] * cv);
+            S[d * vb + c] = s;
+            acc = fmaf(s, qs[d], acc);
+        }
+        red[threadIdx.x] = acc;
+        __syncthreads();
+        if (threadIdx.x < vb && col_ok) {
+            float o = 0.0f;
+            for (int i = 0; i < ng; ++i) o += red[i * vb + threadIdx.x];
+            out[tok * a.out_stride + (size_t)h * V + v0 + c] = fmaf(skip, vv, o);
+        }
+    }
+    if (col_ok)
+        for (int d = g; d < D; d += ng) sp[(size_t)d * V + c] = S[d * vb + c];
+}
+
+extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_off, const void* vsrc, long v_stride,
+                              int v_off, const void* raw, long r_stride, int r_off, int dtype, float* out,
+                              long out_stride, float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs,
+                              int H, int D, int V, int heads_per_group, int mode, float q_scale, float inv_tau,
+                              const float* bias, const float* rate, const float* skip, int few_tokens,
+                              cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype), "decay_scan: unknown dtype code %d", dtype);
+    BFI_REQUIRE(H > 0 && D > 0 && V > 0, "decay_scan: bad sizes heads=%d dim=%d vdim=%d", H, D, V);
+    BFI_REQUIRE(heads_per_group > 0 && H % heads_per_group == 0, "decay_scan: %d heads do not form groups of %d", H,
+                heads_per_group);
+    BFI_REQUIRE(mode == REC_DECAY_STEP || mode == REC_DECAY_SIGMOID, "decay_scan: unknown decay form %d", mode);
+    BFI_REQUIRE(bias != nullptr && (mode != REC_DECAY_STEP || rate != nullptr), "decay_scan: the decay's constants are missing");
+    BFI_REQUIRE(out_stride >= (long)H * V, "decay_scan: output stride shorter than the heads");
+    if (n_seqs <= 0) return 0;
+    RecArgs a;
+    a.qk_stride = qk_stride, a.v_stride = v_stride, a.r_stride = r_stride, a.out_stride = out_stride;
+    a.q_off = q_off, a.k_off = k_off, a.v_off = v_off, a.r_off = r_off;
+    a.H = H, a.D = D, a.V = V, a.heads_per_group = heads_per_group, a.mode = mode;
+    a.q_scale = q_scale, a.inv_tau = inv_tau, a.bias = bias, a.rate = rate, a.skip = skip;
+    a.cu_seqlens = cu_seqlens, a.seq_slot = seq_slot;
+    // columns per block: few where the step is short (more blocks share the state's traffic)
+    int vb = V;
+    const int want = few_tokens ? 16 : 32;
+    if (V > want) vb = want;
+    const int v_blocks = (V + vb - 1) / vb;
+    int threads = vb * (256 / vb > 0 ? 256 / vb : 1);
+    if (threads < 32) threads = vb * ((32 + vb - 1) / vb);
+    a.vb = vb, a.v_blocks = v_blocks;
+    BFI_REQUIRE((long)H * v_blocks <= 2147483647L && n_seqs <= 65535, "decay_scan: too many heads or sequences for one launch");
+    const size_t smem = ((size_t)D * vb + 3 * (size_t)D + threads) * sizeof(float);
+    BFI_REQUIRE(smem <= 200 * 1024, "decay_scan: a state tile of %d x %d does not fit shared memory", D, vb);
+    cudaError_t e = cudaSuccess;
+    if (dtype == BFI_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(decay_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            bfi_launch(decay_scan_kernel<float>, dim3(H * v_blocks, n_seqs), dim3(threads), smem, stream, (const float*)qk,
+                       (const float*)vsrc, (const float*)raw, out, state, a);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(decay_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            bfi_launch(decay_scan_kernel<bf16>, dim3(H * v_blocks, n_seqs), dim3(threads), smem, stream, (const bf16*)qk,
+                       (const bf16*)vsrc, (const bf16*)raw, out, state, a);
+    }
+    if (e != cudaSuccess) return bfi_fail("decay_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    return bfi_check_launch("decay_scan");
+}
+
+// ------------------------------------------------------------------------------------------
+// Causal convolution per channel with silu.  Token t of a sequence reads its own input and the
+// taps-1 before it: rows of this step while they belong to the same sequence, then the kept
+// inputs of earlier steps (state [slots][taps-1][C], oldest first; zero when the slot was taken,
+// which is what stands before a sequence's first token).
+//     y[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * u[t-j, c])
+// conv_forward_kernel computes y; conv_keep_kernel then moves the state on (it must not run
+// before every y of the step has read the old state: it is a launch of its own).  When every
+// sequence brings one token, one thread does both for its channel.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void conv_forward_kernel(const T* __restrict__ u, long u_stride, int u_off, const void* __restrict__ w,
+                                    const void* __restrict__ bias, int w_dtype, float* __restrict__ state,
+                                    T* __restrict__ y, long y_stride, const int* __restrict__ token_slot, int C, int taps,
+                                    int fused_keep) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    const int slot = token_slot[t];
+    if (slot < 0 || ch >= C) return;
+    int own = 0;                                   // rows before t that belong to the same sequence
+    while (own < taps - 1 && t - own - 1 >= 0 && token_slot[t - own - 1] == slot) ++own;
+    float* st = state + (size_t)slot * (taps - 1) * C + ch;
+    float in[REC_MAX_TAPS];
+    float acc = bias ? load_as_f32(bias, w_dtype, ch) : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        in[j] = j <= own ? to_f32(u[(size_t)(t - j) * u_stride + u_off + ch])
+                         : st[(size_t)(taps - 1 + own - j) * C];
+        acc = fmaf(load_as_f32(w, w_dtype, (size_t)ch * taps + (taps - 1 - j)), in[j], acc);
+    }
+    y[(size_t)t * y_stride + ch] = from_f32<T>(rec_silu(acc));
+    if (fused_keep)                                // one token per sequence: the window moves on by one
+        for (int i = 0; i < taps - 1; ++i) st[(size_t)i * C] = in[taps - 2 - i];
+}
+
+template <typename T>
+__global__ void conv_keep_kernel(const T* __restrict__ u, long u_stride, int u_off, float* __restrict__ state,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.x;
+    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    const int slot = seq_slot[seq];
+    if (slot < 0 || ch >= C) return;
+    const int t0 = cu_seqlens[seq], n = cu_seqlens[seq + 1] - t0;
+    float* st = state + (size_t)slot * (taps - 1) * C + ch;
+    float keep[REC_MAX_TAPS];
+    for (int i = 0; i < taps - 1; ++i) {
+        const int r = n - (taps - 1) + i;          // which of the step's tokens lands in place i
+        keep[i] = r >= 0 ? to_f32(u[(size_t)(t0 + r) * u_stride + u_off + ch]) : st[(size_t)(i + n) * C];
+    }
+    for (int i = 0; i < taps - 1; ++i) st[(size_t)i * C] = keep[i];
+}
+
+extern "C" int bfi_causal_conv(const void* u, long u_stride, int u_off, int dtype, const void* w, const void* bias,
+                               int w_dtype, float* state, void* y, long y_stride, const int* token_slot,
+                               const int* cu_seqlens, const int* seq_slot, int n_tokens, int n_seqs, int C, int taps,
+                               int single_tokens, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "causal_conv: unknown dtype code");
+    BFI_REQUIRE(C > 0 && taps >= 1 && taps <= REC_MAX_TAPS, "causal_conv: %d channels, %d taps (at most %d)", C, taps, REC_MAX_TAPS);
+    BFI_REQUIRE(u_stride >= u_off + C && y_stride >= C, "causal_conv: row stride shorter than the channels");
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    const int threads = 128;
+    const dim3 grid_t(n_tokens, (C + threads - 1) / threads), grid_s(n_seqs, (C + threads - 1) / threads);
+    BFI_REQUIRE(grid_t.y <= 65535, "causal_conv: %d channels are too many for one launch", C);
+    const int fused = single_tokens ? 1 : 0;
+    if (dtype == BFI_F32)
+        bfi_launch(conv_forward_kernel<float>, grid_t, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, w, bias, w_dtype,
+                   state, (float*)y, y_stride, token_slot, C, taps, fused);
+    else
+        bfi_launch(conv_forward_kernel<bf16>, grid_t, dim3(threads), 0, stream, (const bf16*)u, u_stride, u_off, w, bias, w_dtype,
+                   state, (bf16*)y, y_stride, token_slot, C, taps, fused);
+    int rc = bfi_check_launch("causal_conv");
+    if (rc || fused || taps == 1) return rc;
+    if (dtype == BFI_F32)
+        bfi_launch(conv_keep_kernel<float>, grid_s, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, state, cu_seqlens,
+                   seq_slot, C, taps);
+    else
+        bfi_launch(conv_keep_kernel<bf16>, grid_s, dim3(threads), 0, stream, (const bf16*)u, u_stride, u_off, state, cu_seqlens,
+                   seq_slot, C, taps);
+    return bfi_check_launch("causal_conv (state)");
+}
+
+// ------------------------------------------------------------------------------------------
+// The gate and the norm after a recurrence.  A row of `width` values is cut into `parts` equal
+// parts, each divided by its own root mean square; the weight has `w_len` values and repeats
+// along the row (w_len = width: one weight per value; w_len = width / parts: shared by the parts).
+//     gate_first:  y = norm_parts(x * act(gate)) * w          otherwise:  y = norm_parts(x) * w * act(gate)
+// act is sigmoid (0) or silu (1).  x float32; gate and y in the activation storage type.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ x, long x_stride, const T* __restrict__ gate,
+                                        long gate_stride, const void* __restrict__ w, int w_dtype, int w_len,
+                                        T* __restrict__ y, long y_stride, int width, int parts, int gate_first,
+                                        int gate_act, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int len = width / parts;
+    const float* xr = x + (size_t)t * x_stride;
+    const T* gr = gate + (size_t)t * gate_stride;
+    T* yr = y + (size_t)t * y_stride;
+    for (int p = warp; p < parts; p += n_warps) {
+        const int j0 = p * len;
+        float ss = 0.0f;
+        for (int j = lane; j < len; j += 32) {
+            float v = xr[j0 + j];
+            if (gate_first) {
+                const float gv = to_f32(gr[j0 + j]);
+                v *= gate_act ? rec_silu(gv) : rec_sigmoid(gv);
+            }
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)len + eps);
+        for (int j = lane; j < len; j += 32) {
+            const float gv = to_f32(gr[j0 + j]);
+            const float ga = gate_act ? rec_silu(gv) : rec_sigmoid(gv);
+            yr[j0 + j] = from_f32<T>(xr[j0 + j] * ga * scale * load_as_f32(w, w_dtype, (j0 + j) % w_len));
+        }
+    }
+}
+
+extern "C" int bfi_gated_group_norm(const float* x, long x_stride, const void* gate, long gate_stride, int dtype,
+                                    const void* w, int w_dtype, int w_len, void* y, long y_stride, int n_rows, int width,
+                                    int parts, int gate_first, int gate_act, float eps, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "gated_group_norm: unknown dtype code");
+    BFI_REQUIRE(n_rows >= 0 && width > 0 && parts > 0 && width % parts == 0,
+                "gated_group_norm: a row of %d values does not cut into %d equal parts", width, parts);
+    BFI_REQUIRE(w_len > 0 && width % w_len == 0, "gated_group_norm: a weight of %d values does not repeat along %d", w_len, width);
+    BFI_REQUIRE(x_stride >= width && gate_stride >= width && y_stride >= width, "gated_group_norm: row stride shorter than the row");
+    if (n_rows == 0) return 0;
+    int warps = parts < 8 ? parts : 8;
+    if (dtype == BFI_F32)
+        bfi_launch(gated_group_norm_kernel<float>, dim3(n_rows), dim3(32 * warps), 0, stream, x, x_stride, (const float*)gate,
+                   gate_stride, w, w_dtype, w_len, (float*)y, y_stride, width, parts, gate_first, gate_act, eps);
+    else
+        bfi_launch(gated_group_norm_kernel<bf16>, dim3(n_rows), dim3(32 * warps), 0, stream, x, x_stride, (const bf16*)gate,
+                   gate_stride, w, w_dtype, w_len, (bf16*)y, y_stride, width, parts, gate_first, gate_act, eps);
+    return bfi_check_launch("gated_group_norm");
+}
+
+BFI_TRACE_EXPORT(recurrence)

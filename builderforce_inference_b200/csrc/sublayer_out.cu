@@ -1,0 +1,71 @@
+// What happens to a sublayer's output on its way into the residual stream when the block does more
+// than add it: a norm of the output before the add, and a weighted sum of two outputs.
+//
+//   bfi_norm_add:      x[t, :] += y[t, :] * rsqrt(mean(y[t, :]^2) + eps) * w        (y float32)
+//   bfi_weighted_sum:  out[t, :] = a * y0[t, :] + b * y1[t, :]                      (all float32)
+//   bfi_scale_rows:    x[r, :] *= s                                                 (float32)
+//
+// The residual stream x and the sublayer outputs are float32 in every run dtype; the weight is
+// float32 or bfloat16.  All arithmetic is float32.
+#include "common.cuh"
+
+__global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride,
+                                const void* __restrict__ w, int w_dtype, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const float* yr = y + (size_t)t * y_stride;
+    float* xr = x + (size_t)t * x_stride;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) xr[j] += yr[j] * scale * load_as_f32(w, w_dtype, j);
+}
+
+extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stride, const void* w, int w_dtype,
+                            int n_rows, int width, float eps, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(w_dtype), "norm_add: unknown dtype code %d", w_dtype);
+    BFI_REQUIRE(n_rows >= 0 && width > 0, "norm_add: bad sizes rows=%d width=%d", n_rows, width);
+    BFI_REQUIRE(x_stride >= width && y_stride >= width, "norm_add: row stride shorter than the row");
+    if (n_rows == 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps);
+    return bfi_check_launch("norm_add");
+}
+
+__global__ void weighted_sum_kernel(float* __restrict__ out, const float* __restrict__ y0, float a,
+                                    const float* __restrict__ y1, float b, long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a * y0[i] + b * y1[i];
+}
+
+extern "C" int bfi_weighted_sum(float* out, const float* y0, float a, const float* y1, float b, long n,
+                                cudaStream_t stream) {
+    BFI_REQUIRE(n >= 0, "weighted_sum: negative size");
+    if (n == 0) return 0;
+    bfi_launch(weighted_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, out, y0, a, y1, b, n);
+    return bfi_check_launch("weighted_sum");
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ x, long stride, int cols, float s) {
+    pdl_trigger();
+    pdl_wait();
+    float* r = x + (size_t)blockIdx.y * stride;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < cols) r[j] *= s;
+}
+
+// x[r, :] *= s over float32 rows (the logits' scale)
+extern "C" int bfi_scale_rows(float* x, long stride, int n_rows, int cols, float s, cudaStream_t stream) {
+    BFI_REQUIRE(n_rows >= 0 && cols > 0 && stride >= cols, "scale_rows: bad sizes rows=%d cols=%d", n_rows, cols);
+    if (n_rows == 0) return 0;
+    BFI_REQUIRE(n_rows <= 65535, "scale_rows: %d rows are too many for one launch", n_rows);
+    bfi_launch(scale_rows_kernel, dim3((cols + 255) / 256, n_rows), dim3(256), 0, stream, x, stride, cols, s);
+    return bfi_check_launch("scale_rows");
+}
+
+BFI_TRACE_EXPORT(sublayer_out)

@@ -147,3 +147,5 @@ class Decoder:
         """Final norm and head at the given rows of ``x``; ``out`` is float32 ``[len(rows), vocab]``."""
         h = self.final_norm.forward(ctx, x, rows, tag="head.norm")
         linear(h, self.head, out, EPI_STORE)
+        if self.spec.logit_scale != 1.0:
+            ops.scale_rows(out, float(self.spec.logit_scale))

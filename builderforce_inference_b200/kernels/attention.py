@@ -8,6 +8,9 @@ import torch
 def attend(ctx, qkv, out, kv, n_heads: int, scale: float, sink=None) -> bool:
     if qkv.dtype != torch.bfloat16:
         return False
+    if not kv.plain or isinstance(sink, torch.Tensor):
+        # values of another size than the keys, a chunked mask, a learned sink per head: the general kernel
+        return False
     from . import fast_ops
     if ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs:
         return fast_ops.attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale, sink=sink)

@@ -194,7 +194,7 @@ def qk_prepare(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, token_pos:
                token_slot: torch.Tensor, kv, flags: int, *, q_bias=None, k_bias=None, v_bias=None,
                q_norm_w=None, k_norm_w=None, norm_mode: int = NORM_NONE, eps: float = 1e-6, rope_table=None,
                rot_dim: int = 0, pairing: int = PAIR_HALF, residual=None, out_bias=None,
-               status: Optional[torch.Tensor] = None) -> None:
+               status: Optional[torch.Tensor] = None, v_dim: Optional[int] = None) -> None:
     """Between the q/k(/v) projection and the attention, one block per token: biases, the values
     (the row's own v heads, or with ``FLAG_VALUES_ARE_KEYS`` the keys as they stand after their
     bias), a norm per head or over the whole projection, the rotation with either pairing, q back in
@@ -205,15 +205,16 @@ def qk_prepare(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, token_pos:
     _i32(token_slot, "token slots")
     n_tokens = qkv.shape[0]
     own_v = not (flags & FLAG_VALUES_ARE_KEYS)
+    v_dim = head_dim if v_dim is None else int(v_dim)
     if token_pos.numel() < n_tokens or token_slot.numel() < n_tokens:
         raise KernelError("qk_prepare: position/slot arrays shorter than the tokens")
-    if qkv.shape[1] != (n_q + (2 if own_v else 1) * n_kv) * head_dim:
+    if qkv.shape[1] != (n_q + n_kv) * head_dim + (n_kv * v_dim if own_v else 0):
         raise KernelError(f"qk_prepare: a row of {qkv.shape[1]} values does not hold the heads")
     bias_dt = norm_dt = 0
-    for b, n in ((q_bias, n_q), (k_bias, n_kv), (v_bias, n_kv)):
+    for b, n in ((q_bias, n_q * head_dim), (k_bias, n_kv * head_dim), (v_bias, n_kv * v_dim)):
         if b is not None:
-            if b.shape != (n * head_dim,) or not b.is_contiguous():
-                raise KernelError(f"qk_prepare: a projection bias must be [{n * head_dim}]")
+            if b.shape != (n,) or not b.is_contiguous():
+                raise KernelError(f"qk_prepare: a projection bias must be [{n}]")
             bias_dt = dtype_code(b.dtype)
     if len({b.dtype for b in (q_bias, k_bias, v_bias) if b is not None}) > 1:
         raise KernelError("qk_prepare: the projection biases must share a dtype")
@@ -234,7 +235,7 @@ def qk_prepare(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, token_pos:
     k_pages = v_pages = table = None
     stride = 0
     if kv is not None and (flags & FLAG_WRITE_CACHE):
-        if kv.k.dtype != qkv.dtype or kv.n_kv_heads != n_kv or kv.head_dim != head_dim:
+        if kv.k.dtype != qkv.dtype or kv.n_kv_heads != n_kv or kv.head_dim != head_dim or kv.value_dim != v_dim:
             raise KernelError("cache pages do not fit the heads being written")
         k_pages, v_pages, table = kv.k, kv.v, kv.block_table
         stride = table.stride(0)
@@ -246,7 +247,7 @@ def qk_prepare(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, token_pos:
         width, r_stride, ob_dt = residual.shape[1], residual.stride(0), dtype_code(out_bias.dtype)
     library("core").call(
         "bfi_qk_prepare", _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_long(qkv.stride(0)), c_int(n_tokens), c_int(n_q),
-        c_int(n_kv), c_int(head_dim), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), c_int(bias_dt), _ptr(q_norm_w),
+        c_int(n_kv), c_int(head_dim), c_int(v_dim), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), c_int(bias_dt), _ptr(q_norm_w),
         _ptr(k_norm_w), c_int(norm_dt), c_int(norm_mode), c_float(eps), _ptr(rope_table), c_int(rot_dim),
         c_int(positions), c_int(pairing), _ptr(token_pos), _ptr(token_slot), _ptr(k_pages), _ptr(v_pages), _ptr(table),
         c_int(stride), c_int(flags), _ptr(residual if out_bias is not None else None), c_long(r_stride), _ptr(out_bias),
@@ -303,10 +304,19 @@ def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: flo
 
 def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_seqlens: torch.Tensor,
                     seq_slot: torch.Tensor, seq_start: torch.Tensor, n_seqs: int, max_tokens: int,
-                    n_q: int, scale: float, sink: Optional[float] = None) -> None:
+                    n_q: int, scale: float, sink=None) -> None:
     """``q`` is the first query element of the step (a view into the qkv buffer); token ``t``, head
-    ``h`` lies at ``q + t*q_stride + h*head_dim``.  ``out`` is ``[tokens, n_q*head_dim]``.  With
-    ``sink`` the softmax's denominator carries ``exp(sink)`` beside the keys' terms."""
+    ``h`` lies at ``q + t*q_stride + h*head_dim``.  ``out`` is ``[tokens, n_q*v_dim]``.  With
+    ``sink`` (a number, or a float32 tensor with one per query head) the softmax's denominator
+    carries ``exp(sink)`` beside the keys' terms.  The cache view says whether the values have a
+    size of their own and whether a token reads only its own chunk of positions."""
+    has_sink, sink_value, sinks = 0, 0.0, None
+    if isinstance(sink, torch.Tensor):
+        if sink.dtype != torch.float32 or not sink.is_contiguous() or sink.numel() != n_q or not sink.is_cuda:
+            raise KernelError(f"attention: a sink per head must be contiguous float32 [{n_q}] on the GPU")
+        has_sink, sinks = 2, sink
+    elif sink is not None:
+        has_sink, sink_value = 1, float(sink)
     _need_cuda(q, out, cu_seqlens, seq_slot, seq_start)
     _rows_2d(out, "attention output")
     _i32(cu_seqlens, "cu_seqlens")
@@ -318,8 +328,206 @@ def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_se
         "bfi_attention_paged", _ptr(q), c_int(dtype_code(q.dtype)), c_long(q_stride), _ptr(out),
         c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)),
         _ptr(cu_seqlens), _ptr(seq_slot), _ptr(seq_start), c_int(n_seqs), c_int(max_tokens), c_int(n_q),
-        c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(kv.window or 0), c_float(scale),
-        c_int(0 if sink is None else 1), c_float(0.0 if sink is None else sink), _stream())
+        c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(kv.value_dim), c_int(kv.window or 0), c_int(kv.chunk or 0),
+        c_float(scale), c_int(has_sink), c_float(sink_value), _ptr(sinks), _stream())
+
+
+def _f32_vector(t: Optional[torch.Tensor], n: int, what: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n or not t.is_cuda):
+        raise KernelError(f"{what} must be contiguous float32 [{n}] on the GPU")
+
+
+def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> None:
+    """``x[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w``: a sublayer's output, normed, into the
+    float32 residual stream."""
+    _need_cuda(x, y, w)
+    _rows_2d(x, "residual stream")
+    _rows_2d(y, "sublayer output")
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape:
+        raise KernelError("norm_add: the residual stream and the sublayer output must be float32 of one shape")
+    if w.shape != (x.shape[1],) or not w.is_contiguous():
+        raise KernelError(f"norm_add: weight must be [{x.shape[1]}]")
+    library("core").call("bfi_norm_add", _ptr(x), c_long(x.stride(0)), _ptr(y), c_long(y.stride(0)), _ptr(w),
+                         c_int(dtype_code(w.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps), _stream())
+
+
+def weighted_sum(out: torch.Tensor, y0: torch.Tensor, a: float, y1: torch.Tensor, b: float) -> None:
+    """``out = a * y0 + b * y1`` over contiguous float32 tensors of one shape."""
+    _need_cuda(out, y0, y1)
+    for t in (out, y0, y1):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != out.shape:
+            raise KernelError("weighted_sum: contiguous float32 tensors of one shape")
+    library("core").call("bfi_weighted_sum", _ptr(out), _ptr(y0), c_float(a), _ptr(y1), c_float(b), c_long(out.numel()),
+                         _stream())
+
+
+def scale_rows(x: torch.Tensor, s: float) -> None:
+    """``x *= s`` over float32 rows."""
+    _need_cuda(x)
+    _rows_2d(x, "rows")
+    if x.dtype != torch.float32:
+        raise KernelError("scale_rows: float32 rows")
+    library("core").call("bfi_scale_rows", _ptr(x), c_long(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]),
+                         c_float(s), _stream())
+
+
+DECAY_STEP, DECAY_SIGMOID = 1, 2
+
+
+def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off: int, raw: torch.Tensor, r_off: int,
+               out: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
+               n_heads: int, dim: int, vdim: int, heads_per_group: int, mode: int, bias: torch.Tensor,
+               rate: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None, q_scale: float = 1.0,
+               inv_tau: float = 1.0, few_tokens: bool = False) -> None:
+    """A linear recurrence whose decay depends on the token, over the step's new tokens:
+    ``S = diag(a) S + k (c v)^T; o = S^T q + skip * v`` with ``S`` float32
+    ``[slots, heads, dim, vdim]`` carried in ``state``.  q and k are columns of ``qk`` (group
+    ``h // heads_per_group`` of head ``h``), v of ``v``, the decay's raw value of ``raw`` (rows of one
+    storage type).  ``DECAY_STEP``: ``c = softplus(raw_h + bias_h)``, ``a = exp(-rate_h c)``;
+    ``DECAY_SIGMOID``: ``a_d = sigmoid(raw_hd + bias_hd)^inv_tau``, ``c = 1``.  ``out`` float32."""
+    _need_cuda(qk, v, raw, out, state, cu_seqlens, seq_slot, bias, rate, skip)
+    for t, what in ((qk, "q and k"), (v, "values"), (raw, "decay input"), (out, "recurrence output")):
+        _rows_2d(t, what)
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(seq_slot, "sequence slots")
+    if not (qk.dtype == v.dtype == raw.dtype):
+        raise KernelError("decay_scan: q, k, v and the decay input must share a storage type")
+    if out.dtype != torch.float32 or out.shape[1] != n_heads * vdim:
+        raise KernelError("decay_scan: the output must be float32 [tokens, heads * vdim]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, dim, vdim):
+        raise KernelError("decay_scan: the state must be contiguous float32 [slots, heads, dim, vdim]")
+    groups = n_heads // max(1, heads_per_group)
+    if max(q_off, k_off) + groups * dim > qk.shape[1] or v_off + n_heads * vdim > v.shape[1]:
+        raise KernelError("decay_scan: a row is shorter than the heads")
+    n_raw = n_heads if mode == DECAY_STEP else n_heads * dim
+    if r_off + n_raw > raw.shape[1]:
+        raise KernelError("decay_scan: the decay input's row is shorter than the heads")
+    _f32_vector(bias, n_raw, "decay_scan: the decay's bias")
+    _f32_vector(rate, n_heads, "decay_scan: the decay's rate")
+    _f32_vector(skip, n_heads, "decay_scan: the skip factor")
+    library("core").call("bfi_decay_scan", _ptr(qk), c_long(qk.stride(0)), c_int(q_off), c_int(k_off), _ptr(v),
+                         c_long(v.stride(0)), c_int(v_off), _ptr(raw), c_long(raw.stride(0)), c_int(r_off),
+                         c_int(dtype_code(qk.dtype)), _ptr(out), c_long(out.stride(0)), _ptr(state), _ptr(cu_seqlens),
+                         _ptr(seq_slot), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), c_int(heads_per_group),
+                         c_int(mode), c_float(q_scale), c_float(inv_tau), _ptr(bias), _ptr(rate), _ptr(skip),
+                         c_int(1 if few_tokens else 0), _stream())
+
+
+def causal_conv(u: torch.Tensor, u_off: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, y: torch.Tensor, token_slot: torch.Tensor, cu_seqlens: torch.Tensor,
+                seq_slot: torch.Tensor, n_seqs: int, single_tokens: bool = False) -> None:
+    """``y[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] u[t-j, u_off + c])`` within each sequence; the
+    inputs before a step's first token come from ``state`` (float32 ``[slots, taps-1, channels]``,
+    oldest first), which is then moved on by the step's tokens."""
+    _need_cuda(u, w, bias, state, y, token_slot, cu_seqlens, seq_slot)
+    _rows_2d(u, "convolution input")
+    _rows_2d(y, "convolution output")
+    _i32(token_slot, "token slots")
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(seq_slot, "sequence slots")
+    taps = w.shape[1] if w.dim() == 2 else 0
+    if w.shape != (channels, taps) or not w.is_contiguous() or taps < 1:
+        raise KernelError(f"causal_conv: weights must be contiguous [{channels}, taps]")
+    if bias is not None and (bias.shape != (channels,) or bias.dtype != w.dtype or not bias.is_contiguous()):
+        raise KernelError(f"causal_conv: bias must be [{channels}] of the weights' dtype")
+    if u.dtype != y.dtype or y.shape != (u.shape[0], channels) or u_off + channels > u.shape[1]:
+        raise KernelError("causal_conv: input and output must share a dtype; output [tokens, channels]")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (max(taps - 1, 0), channels):
+        raise KernelError("causal_conv: the state must be contiguous float32 [slots, taps-1, channels]")
+    library("core").call("bfi_causal_conv", _ptr(u), c_long(u.stride(0)), c_int(u_off), c_int(dtype_code(u.dtype)),
+                         _ptr(w), _ptr(bias), c_int(dtype_code(w.dtype)), _ptr(state), _ptr(y), c_long(y.stride(0)),
+                         _ptr(token_slot), _ptr(cu_seqlens), _ptr(seq_slot), c_int(u.shape[0]), c_int(n_seqs),
+                         c_int(channels), c_int(taps), c_int(1 if single_tokens else 0), _stream())
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gated_group_norm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor, parts: int,
+                     gate_first: bool, gate_act: int = GATE_SILU) -> None:
+    """A row cut into ``parts`` equal parts, each divided by its own root mean square, times ``w``
+    (which repeats along the row when shorter), with a gate ``act(gate)`` applied before the norm
+    (``gate_first``) or after it.  ``x`` float32; ``gate`` and ``out`` in the activation dtype."""
+    _need_cuda(x, gate, w, out)
+    _rows_2d(x, "norm input")
+    _rows_2d(gate, "gate")
+    _rows_2d(out, "norm output")
+    n, width = x.shape
+    if x.dtype != torch.float32 or gate.dtype != out.dtype or gate.shape != (n, width) or out.shape != (n, width):
+        raise KernelError("gated_group_norm: x float32 [rows, width]; gate and output [rows, width] of one dtype")
+    if w.dim() != 1 or not w.is_contiguous():
+        raise KernelError("gated_group_norm: the weight must be a contiguous vector")
+    library("core").call("bfi_gated_group_norm", _ptr(x), c_long(x.stride(0)), _ptr(gate), c_long(gate.stride(0)),
+                         c_int(dtype_code(out.dtype)), _ptr(w), c_int(dtype_code(w.dtype)), c_int(w.numel()), _ptr(out),
+                         c_long(out.stride(0)), c_int(n), c_int(width), c_int(parts), c_int(1 if gate_first else 0),
+                         c_int(gate_act), c_float(eps), _stream())
+
+
+def moe_route(z: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor], idx: torch.Tensor,
+              weight: torch.Tensor, top: int, n_groups: int = 1, keep: int = 1, weight_scale: float = 1.0,
+              gate: Optional[torch.Tensor] = None) -> None:
+    """The router's decision per token from float32 logits ``z[:, :n_experts]``: softmax, choice
+    scores ``s + correction``, the ``keep`` best of ``n_groups`` groups, the ``top`` best experts of
+    those; ``idx`` int32 and ``weight`` float32 ``[tokens, top]`` (the chosen ``s`` times
+    ``weight_scale``).  With ``gate`` (float32 ``[tokens]``): ``sigmoid(z[:, n_experts])``."""
+    _need_cuda(z, correction, idx, weight, gate)
+    _rows_2d(z, "router logits")
+    n = z.shape[0]
+    if z.dtype != torch.float32:
+        raise KernelError("moe_route: the logits must be float32")
+    _f32_vector(correction, n_experts, "moe_route: the correction")
+    if idx.dtype != torch.int32 or not idx.is_contiguous() or idx.shape != (n, top) or weight.dtype != torch.float32 \
+            or not weight.is_contiguous() or weight.shape != (n, top):
+        raise KernelError("moe_route: idx int32 and weight float32, both contiguous [tokens, top]")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.numel() < n):
+        raise KernelError("moe_route: the gate must be contiguous float32 [tokens]")
+    library("core").call("bfi_moe_route", _ptr(z), c_long(z.stride(0)), _ptr(correction), _ptr(idx), _ptr(weight), _ptr(gate),
+                         c_int(n), c_int(n_experts), c_int(top), c_int(n_groups), c_int(keep), c_float(weight_scale),
+                         c_int(0 if gate is None else 1), _stream())
+
+
+def moe_gate_up(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, token_slot: torch.Tensor,
+                act: torch.Tensor) -> None:
+    """``act[t, k] = silu(w_gate[e] h_t) * (w_up[e] h_t)`` with ``e = idx[t, k]``; the weights are
+    ``[experts, ff, width]``, ``act`` ``[tokens * top, ff]``."""
+    _need_cuda(h, w_gate, w_up, idx, token_slot, act)
+    _rows_2d(h, "feed-forward input")
+    n, width = h.shape
+    top = idx.shape[1]
+    ff = w_gate.shape[1]
+    if w_gate.dim() != 3 or w_gate.shape != w_up.shape or w_gate.shape[2] != width or not w_gate.is_contiguous() \
+            or not w_up.is_contiguous() or w_gate.dtype != h.dtype or w_up.dtype != h.dtype:
+        raise KernelError("moe_gate_up: expert weights must be contiguous [experts, ff, width] of the input's dtype")
+    if act.dtype != h.dtype or not act.is_contiguous() or act.shape != (n * top, ff):
+        raise KernelError("moe_gate_up: the output must be contiguous [tokens * top, ff] of the input's dtype")
+    _i32(idx, "expert choices")
+    _i32(token_slot, "token slots")
+    library("core").call("bfi_moe_gate_up", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_gate), _ptr(w_up),
+                         _ptr(idx), _ptr(token_slot), _ptr(act), c_int(n), c_int(top), c_int(width), c_int(ff), _stream())
+
+
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, token_slot: torch.Tensor,
+             out: torch.Tensor, shared_out: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+             accumulate: bool = False) -> None:
+    """``out[t] (= | +=) sum_k weight[t, k] * w_down[idx[t, k]] act[t, k] + gate[t] * shared_out[t]``
+    (the last term only with ``shared_out``; ``gate`` None is 1); ``w_down`` ``[experts, width, ff]``,
+    ``out`` float32 ``[tokens, width]``."""
+    _need_cuda(act, w_down, idx, weight, token_slot, out, shared_out, gate)
+    _rows_2d(out, "feed-forward output")
+    n, top = idx.shape
+    width, ff = w_down.shape[1], w_down.shape[2]
+    if w_down.dim() != 3 or not w_down.is_contiguous() or w_down.dtype != act.dtype:
+        raise KernelError("moe_down: expert weights must be contiguous [experts, width, ff] of the activations' dtype")
+    if not act.is_contiguous() or act.shape != (n * top, ff):
+        raise KernelError("moe_down: the activations must be contiguous [tokens * top, ff]")
+    if out.dtype != torch.float32 or out.shape != (n, width):
+        raise KernelError("moe_down: the output must be float32 [tokens, width]")
+    if shared_out is not None and (shared_out.dtype != torch.float32 or shared_out.shape != (n, width) or shared_out.stride(1) != 1):
+        raise KernelError("moe_down: the shared output must be float32 [tokens, width]")
+    library("core").call("bfi_moe_down", _ptr(act), c_int(dtype_code(act.dtype)), _ptr(w_down), _ptr(idx), _ptr(weight),
+                         _ptr(token_slot), _ptr(shared_out), c_long(0 if shared_out is None else shared_out.stride(0)),
+                         _ptr(gate), _ptr(out), c_long(out.stride(0)), c_int(n), c_int(top), c_int(width), c_int(ff),
+                         c_int(1 if accumulate else 0), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:

@@ -2,7 +2,7 @@
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, FeedForward, KVNeed,
                    LayerSpec, Mixer, ModelSpec, Norm, ParamSpec, Part, PartSpec, PositionEncoding, Registry,
                    RunSpec, StateNeed)
-from . import attention, block, lightning, mlp, norm, rotary  # noqa: F401  (registration)
+from . import attention, block, combine, lightning, mlp, moe, norm, recurrent, rotary  # noqa: F401  (registration)
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "FeedForward",
            "KVNeed", "LayerSpec", "Mixer", "ModelSpec", "Norm", "ParamSpec", "Part", "PartSpec",

@@ -15,7 +15,11 @@ Variants, each a parameter: ``bias`` (q, k, v and output projections carry one);
 whole q projection and over the whole k projection, weights of that size); ``values`` ``"keys"``
 (no v projection: the values are the keys as projected, with their bias, before norm and
 rotation); ``sink`` (a score every query sees beside its keys, with no value: the softmax's
-denominator carries ``exp(sink)``); the position encoding's pairing and partial width.  The plain
+denominator carries ``exp(sink)``; a number, or ``"learned"``: one per query head, a tensor of the
+checkpoint); ``v_dim`` (value heads of another size than the keys'); ``chunk`` (a token reads only
+the keys of its own block of ``chunk`` consecutive positions, blocks counted from position 0);
+``out_bias`` (whether the output projection carries a bias when the others do; default: it does);
+the position encoding's pairing and partial width.  The plain
 combination (no bias, head norm or none, own values, rotate-half) runs the per-head kernel that
 fuses norm, rotation and cache write; the others run the per-token kernel that also adds the
 biases, so no variant costs a launch of its own.
@@ -39,7 +43,8 @@ class Attention(Mixer):
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, qk_norm=False, eps: float = 1e-6,
                  window: Optional[int] = None, scale: Optional[float] = None, own_kv: bool = True,
-                 bias: bool = False, values: str = "projection", sink: Optional[float] = None):
+                 bias: bool = False, values: str = "projection", sink=None, v_dim: Optional[int] = None,
+                 chunk: Optional[int] = None, out_bias: Optional[bool] = None):
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"GQA: {n_heads} query heads do not divide into {n_kv_heads} kv heads")
         if head_dim % 2 != 0 or head_dim > 512:
@@ -54,10 +59,24 @@ class Attention(Mixer):
             raise ValueError("a layer without keys of its own has no keys to use as values")
         if window is not None and window < 1:
             raise ValueError(f"window must be positive, got {window}")
+        if chunk is not None and chunk < 1:
+            raise ValueError(f"chunk must be positive, got {chunk}")
+        v_dim = head_dim if v_dim is None else int(v_dim)
+        if v_dim < 1 or v_dim > 512:
+            raise ValueError(f"attention kernels take value sizes from 1 to 512, got {v_dim}")
+        if values == "keys" and v_dim != head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if not (sink is None or sink == "learned" or isinstance(sink, (int, float))):
+            raise ValueError(f"sink must be a number or 'learned', got {sink!r}")
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.qk_norm, self.eps, self.window = (qk_norm or None), float(eps), window
         self.bias, self.values_are_keys = bool(bias), values == "keys"
-        self.sink = None if sink is None else float(sink)
+        self.v_dim, self.chunk = v_dim, chunk
+        self.out_bias = self.bias if out_bias is None else bool(out_bias)
+        if self.out_bias and not self.bias:
+            raise ValueError("an output bias without the projections' biases is not a known variant")
+        self.learned_sink = sink == "learned"
+        self.sink = None if sink is None or self.learned_sink else float(sink)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.own_kv = bool(own_kv)
         self.position = POSITION_ENCODINGS.build(position) if position is not None \
@@ -70,18 +89,20 @@ class Attention(Mixer):
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, h = self.head_dim, self.width
-        specs = {"q_proj": ParamSpec((self.n_heads * d, h)), "o_proj": ParamSpec((h, self.n_heads * d))}
+        specs = {"q_proj": ParamSpec((self.n_heads * d, h)), "o_proj": ParamSpec((h, self.n_heads * self.v_dim))}
         if self.own_kv:
             specs["k_proj"] = ParamSpec((self.n_kv_heads * d, h))
             if not self.values_are_keys:
-                specs["v_proj"] = ParamSpec((self.n_kv_heads * d, h))
+                specs["v_proj"] = ParamSpec((self.n_kv_heads * self.v_dim, h))
+        if self.learned_sink:
+            specs["sink"] = ParamSpec((self.n_heads,), "matrix")
         if self.qk_norm:
             row = self.qk_norm == "row"
             specs["q_norm"] = ParamSpec((self.n_heads * d if row else d,), "norm")
             if self.own_kv:
                 specs["k_norm"] = ParamSpec((self.n_kv_heads * d if row else d,), "norm")
         if self.bias:
-            for name in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            for name in ("q_proj", "k_proj", "v_proj") + (("o_proj",) if self.out_bias else ()):
                 if name in specs:
                     specs[name + ".bias"] = ParamSpec((specs[name].shape[0],), "matrix")
         return specs
@@ -89,10 +110,11 @@ class Attention(Mixer):
     def _plain(self) -> bool:
         """The combination the per-head kernel (norm, rotate-half, cache write) covers."""
         return not self.bias and not self.values_are_keys and self.qk_norm != "row" \
-            and getattr(self.position, "pairing", "half") == "half"
+            and getattr(self.position, "pairing", "half") == "half" and self.v_dim == self.head_dim
 
     def cache_need(self):
-        return KVNeed(self.n_kv_heads, self.head_dim, self.window)
+        return KVNeed(self.n_kv_heads, self.head_dim, self.window,
+                      v_dim=None if self.v_dim == self.head_dim else self.v_dim, chunk=self.chunk)
 
     def prepare(self, runtime, max_positions: int) -> None:
         self.position.prepare(runtime, max_positions)
@@ -105,17 +127,28 @@ class Attention(Mixer):
             mats = [m.float() for m in mats]
         self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
         self.w_o = tensors["o_proj"]
+        self.sinks = tensors["sink"].float().contiguous() if self.learned_sink else None
         self.q_norm = tensors.get("q_norm")
         self.k_norm = tensors.get("k_norm")
         if self.q_norm is not None and self.k_norm is not None and self.q_norm.dtype != self.k_norm.dtype:
             self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
         if self.bias:
             self.b_q, self.b_k, self.b_v = (tensors.get(n + ".bias") for n in ("q_proj", "k_proj", "v_proj"))
-            self.b_o = tensors["o_proj.bias"]
+            self.b_o = tensors["o_proj.bias"] if self.out_bias else None
             if len({b.dtype for b in (self.b_q, self.b_k, self.b_v) if b is not None}) > 1:
                 self.b_q, self.b_k, self.b_v = (None if b is None else b.float() for b in (self.b_q, self.b_k, self.b_v))
 
     def forward(self, ctx, h, residual, run) -> None:
+        self._run(ctx, h, residual, run, EPI_ACCUMULATE)
+
+    def forward_store(self, ctx, h, out, run) -> None:
+        if self.b_o is not None:       # the output bias is added to the target's row before the product
+            out.zero_()
+            self._run(ctx, h, out, run, EPI_ACCUMULATE)
+        else:
+            self._run(ctx, h, out, run, EPI_STORE)
+
+    def _run(self, ctx, h, residual, run, epilogue) -> None:
         kv = run.kv
         if kv is None:
             raise RuntimeError("attention needs a key/value cache for its run")
@@ -123,7 +156,7 @@ class Attention(Mixer):
         if run.writes_cache != self.own_kv:
             raise RuntimeError("an attention layer writes the cache exactly when it has k and v projections")
         d = self.head_dim
-        qkv = ctx.rows("attn.qkv", (self.n_heads + (1 if self.values_are_keys else 2) * n_kv_in) * d)
+        qkv = ctx.rows("attn.qkv", (self.n_heads + n_kv_in) * d + (0 if self.values_are_keys else n_kv_in * self.v_dim))
         linear(h, self.w_qkv, qkv, EPI_STORE)
 
         fused = self.position.fused_rotary()
@@ -138,7 +171,7 @@ class Attention(Mixer):
                            norm_mode={None: ops.NORM_NONE, "head": ops.NORM_HEAD, "row": ops.NORM_ROW}[self.qk_norm],
                            eps=self.eps, rope_table=table, rot_dim=rot,
                            pairing=ops.PAIR_ADJACENT if getattr(self.position, "pairing", "half") == "adjacent" else ops.PAIR_HALF,
-                           residual=residual, out_bias=self.b_o, status=ctx.status)
+                           residual=residual, out_bias=self.b_o, status=ctx.status, v_dim=self.v_dim)
         elif fused is not None:
             table, rot = fused
             ops.qk_norm_rope_cache(qkv, self.n_heads, n_kv_in, d, self.q_norm, self.k_norm, self.eps,
@@ -154,13 +187,14 @@ class Attention(Mixer):
                 ops.qk_norm_rope_cache(qkv, self.n_heads, n_kv_in, d, None, None, self.eps, None, 0,
                                        ctx.token_pos, ctx.token_slot, kv, write, ctx.status)
 
-        out = ctx.rows("attn.out", self.n_heads * d)
+        out = ctx.rows("attn.out", self.n_heads * self.v_dim)
         self.attend(ctx, qkv, out, kv)
-        linear(out, self.w_o, residual, EPI_ACCUMULATE)
+        linear(out, self.w_o, residual, epilogue)
 
     def attend(self, ctx, qkv, out, kv) -> None:
         from ..kernels import attention as fast_attention
-        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale, self.sink):
+        sink = self.sinks if self.learned_sink else self.sink
+        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale, sink):
             return
         ops.attention_paged(qkv, qkv.stride(0), out, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
-                            ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, self.sink)
+                            ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, sink)

@@ -12,7 +12,8 @@ Contracts (all tensors live on the GPU):
     ``x`` is the float32 residual stream ``[tokens, width]``; ``h`` is in the activation dtype.
     With ``rows`` (int32 indices) only those rows are normalised, in that order.
 ``Mixer.forward(ctx, h, residual, run)``
-    adds the mixer's output for every token of the step into ``residual`` (float32) in place.
+    adds the mixer's output for every token of the step into ``residual`` (float32) in place;
+    ``forward_store(ctx, h, out, run)`` writes it to ``out`` instead.
     ``run`` gives the run's cache (``run.kv`` pages or ``run.state`` rows) and whether this run
     writes it (``run.writes_cache``) or reads another run's.
 ``FeedForward.forward(ctx, h, residual)``
@@ -44,7 +45,8 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class ParamSpec:
-    """One tensor a part wants: its shape and what it is (which decides its random init)."""
+    """One tensor a part wants: its shape and what it is (which decides its random init).  A size
+    of -1 is one that only the checkpoint's tensor gives; the part reads it in ``load``."""
 
     shape: Tuple[int, ...]
     role: str = "matrix"        # "matrix" | "table" | "norm"
@@ -53,11 +55,20 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class KVNeed:
-    """A mixer that keeps keys and values of earlier tokens: all of them, or a window."""
+    """A mixer that keeps keys and values of earlier tokens: all of them, a window (the last
+    ``window`` positions), or the current chunk (the positions of the token's own block of ``chunk``
+    consecutive positions, blocks counted from position 0).  ``v_dim`` is the size of a value head
+    where it differs from the keys' ``head_dim``."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
 
 @dataclass(frozen=True)
@@ -137,10 +148,22 @@ class Mixer(Part):
     def forward(self, ctx, h, residual, run) -> None:
         raise NotImplementedError
 
+    def forward_store(self, ctx, h, out, run) -> None:
+        """The mixer's output written to ``out`` (float32 ``[tokens, width]``) instead of added to
+        the residual stream, for blocks that do something to it before the add.  A mixer whose last
+        product can store overrides this and saves the clearing."""
+        out.zero_()
+        self.forward(ctx, h, out, run)
+
 
 class FeedForward(Part):
     def forward(self, ctx, h, residual) -> None:
         raise NotImplementedError
+
+    def forward_store(self, ctx, h, out) -> None:
+        """As ``Mixer.forward_store``."""
+        out.zero_()
+        self.forward(ctx, h, out)
 
 
 class Block(Part):
@@ -219,3 +242,4 @@ class ModelSpec:
     max_positions: int = 0
     stop_ids: Tuple[int, ...] = ()
     embedding_scale: float = 1.0       # the embedding rows are multiplied by it; the tied head is not
+    logit_scale: float = 1.0           # the logits are multiplied by it

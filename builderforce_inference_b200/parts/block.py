@@ -4,6 +4,10 @@ the mixer's and the feed-forward's last matrix product.
 ``prenorm``   ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (crates/bfi-models/src/qwen3.rs:217-250).
 ``parallel``  one norm, both sublayers read its output: ``h = norm1(x); x += mixer(h) + ffn(h)``;
               the feed-forward may be absent.
+``sandwich``  a norm before and after each sublayer: ``x += norm1b(mixer(norm1(x)));
+              x += norm2b(ffn(norm2(x)))``; the feed-forward (with its two norms) may be absent.
+              The sublayers write their output to a float32 buffer (``forward_store``) and the
+              second norm adds it, normed, into the residual stream in one kernel.
 """
 from __future__ import annotations
 
@@ -57,3 +61,39 @@ class ParallelBlock(Block):
         self._mixer.forward(ctx, h, residual, run)
         if self.ffn is not None:
             self.ffn.forward(ctx, h, residual)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    graph_safe = True
+
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm1b: PartSpec, norm2: PartSpec = None,
+                 ffn: PartSpec = None, norm2b: PartSpec = None):
+        if (ffn is None) != (norm2 is None) or (ffn is None) != (norm2b is None):
+            raise ValueError("a sandwich block has a feed-forward with both of its norms, or none of the three")
+        self.norm1 = NORMS.build(norm1)
+        self._mixer = MIXERS.build(mixer)
+        self.norm1b = NORMS.build(norm1b)
+        self.norm2 = NORMS.build(norm2) if ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(ffn) if ffn is not None else None
+        self.norm2b = NORMS.build(norm2b) if ffn is not None else None
+
+    def children(self):
+        out = {"norm1": self.norm1, "mixer": self._mixer, "norm1b": self.norm1b}
+        if self.ffn is not None:
+            out.update({"norm2": self.norm2, "ffn": self.ffn, "norm2b": self.norm2b})
+        return out
+
+    def mixer(self):
+        return self._mixer
+
+    def forward(self, ctx, residual, run) -> None:
+        import torch
+        y = ctx.rows("sublayer.out", residual.shape[1], torch.float32)
+        h = self.norm1.forward(ctx, residual)
+        self._mixer.forward_store(ctx, h, y, run)
+        self.norm1b.add_to(ctx, residual, y)
+        if self.ffn is not None:
+            h = self.norm2.forward(ctx, residual)
+            self.ffn.forward_store(ctx, h, y)
+            self.norm2b.add_to(ctx, residual, y)

@@ -1,6 +1,8 @@
 """RMS norm: ``y = x * rsqrt(mean(x^2) + eps) * w`` over the last dim, the weight as stored
-(crates/bfi-core/src/cpu.rs:92-122).  The statistics are float32; the input is the float32
-residual stream and the output is in the activation dtype."""
+(crates/bfi-core/src/cpu.rs:92-122), or, with ``offset``, ``offset + w`` (a weight stored around zero
+enters as ``1 + w``; the sum is made once at load, in float32).  The statistics are float32; the
+input is the float32 residual stream and the output is in the activation dtype.  ``add_to`` is the
+same norm applied to a sublayer's float32 output on its way into the residual stream."""
 from __future__ import annotations
 
 from typing import Dict
@@ -13,9 +15,10 @@ from .base import NORMS, Norm, ParamSpec
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, offset: float = 0.0):
         self.width = int(width)
         self.eps = float(eps)
+        self.offset = float(offset)
         self.weight = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -23,9 +26,15 @@ class RMSNorm(Norm):
 
     def load(self, tensors, runtime) -> None:
         self.weight = tensors["weight"]
+        if self.offset != 0.0:
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def forward(self, ctx, x, rows=None, tag: str = "norm.out"):
         n = x.shape[0] if rows is None else rows.numel()
         out = ctx.rows(tag, self.width, n_rows=n)
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+    def add_to(self, ctx, residual, y) -> None:
+        """``residual += norm(y)``: both float32 ``[tokens, width]``."""
+        ops.norm_add(residual, y, self.weight, self.eps)

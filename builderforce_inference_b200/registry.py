@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its model.
 
 A config.json names its architecture under ``architectures[0]`` (a class name such as
-``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``).  Any of them selects the entry; the lookup is
+``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``, ``Bepilorn``).  Any of them selects the entry; the lookup is
 exact and case-sensitive, and an unknown name is answered with the list of known ones, as in
 the reference (crates/bfi-models/src/arch.rs:70-91).
 """
@@ -70,6 +70,10 @@ def _register_builtin() -> None:
     from .config.datasun import DatasunConfig
     register_architecture(("Datasun", "datasun"),
                           Architecture(name="datasun", config_class=DatasunConfig, describe=datasun.describe))
+    from .architectures import bepilorn
+    from .config.bepilorn import BepilornConfig
+    register_architecture(("Bepilorn", "bepilorn"),
+                          Architecture(name="bepilorn", config_class=BepilornConfig, describe=bepilorn.describe))
 
 
 _register_builtin()

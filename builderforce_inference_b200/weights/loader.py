@@ -94,7 +94,8 @@ def check_names(folder: str, have: Mapping[str, Tuple[torch.dtype, Tuple[int, ..
     for n, s in expected.items():
         if n in have:
             dt, shape = have[n]
-            if tuple(shape) != tuple(s.shape):
+            # a size of -1 in the wanted shape is one that only the tensor gives
+            if len(shape) != len(s.shape) or any(w != -1 and w != g for g, w in zip(shape, s.shape)):
                 wrong.append((n, tuple(shape), tuple(s.shape)))
             if stored_dtype_for(run_dtype, dt) is None:
                 bad.append((n, str(dt)))

@@ -104,6 +104,9 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, dtype: torch.dtype,
     scale, offset = fill_constants(spec.role)
     n = 1
     for d in spec.shape:
+        if d < 0:
+            raise ValueError(f"random weights: a size of tensor '{name}' is left to the checkpoint ({list(spec.shape)}); "
+                             "the configuration must name it")
         n *= d
     if device.type != "cuda":
         values = torch.from_numpy(random_values_cpu(n, key, scale, offset)).reshape(spec.shape)
