@@ -20,7 +20,10 @@ at batch 1 and 32 behind 2,048-token prompts and a 2,048-token prompt) and print
 ``--design datasun`` leaves the benchmark aside and runs the Datasun design (parallel blocks,
 three lightning-attention layers to one windowed softmax-attention layer) beside Qwen3 at equal
 layer sizes, a few sizes, random weights: a 2,048-token prompt with its breakdown by kernel class,
-and decode at batch 8 and 64 behind 1,024-token prompts.  One line.
+and decode at batch 8 and 64 behind 1,024-token prompts.  One line.  ``--design bepilorn`` does
+the same for the Bepilorn design (three state-space layers to one pair of chunked sink attention
+and gated linear attention, a routed feed-forward) beside Datasun and Qwen3, with the milliseconds
+of every kernel of a prompt step and of a single-token step.
 
 The work is one GPU's: for ``--gpus`` above 1 it says so and exits with 2.  The reference arm
 (``--impl reference``) is unavailable: the reference is a Rust workspace, there is no Rust
@@ -205,10 +208,11 @@ def prefill_flops(c, layers, lens):
     return layers * (per_layer + attn) + 2 * h * c["vocab_size"] * len(lens)
 
 
-KERNEL_CLASSES = (("products", ("gemm", "skinny")), ("attention", ("attention",)), ("recurrence", ("lightning",)))
+KERNEL_CLASSES = (("products", ("gemm", "skinny")), ("attention", ("attention",)),
+                  ("recurrence", ("lightning", "decay_scan", "causal_conv")), ("experts", ("moe_",)))
 
 
-def prefill_breakdown(eng, step):
+def prefill_breakdown(eng, step, by_kernel=False):
     """One instrumented prompt step: a CUDA event before and after every kernel, so the kernels run
     strictly one after the other (an event between two launches ends their overlap).  Returns the
     milliseconds by kernel class, the time between kernels (the GPU waiting for the host), and the
@@ -245,10 +249,15 @@ def prefill_breakdown(eng, step):
     out = {k: round(v, 3) for k, v in out.items()}
     out["instrumented_ms"] = round(whole, 3)
     out["kernels"] = len(marks)
+    if by_kernel:
+        names = {}
+        for name, e0, e1 in marks:
+            names[name] = names.get(name, 0.0) + e0.elapsed_time(e1)
+        out["by_kernel_ms"] = {k.replace("bfi_", ""): round(v, 3) for k, v in sorted(names.items(), key=lambda kv: -kv[1])}
     return out
 
 
-def prefill_run(model, tokens, reps, layers, c=None, lens=None, breakdown=False):
+def prefill_run(model, tokens, reps, layers, c=None, lens=None, breakdown=False, by_kernel=False):
     import torch
     from builderforce_inference_b200.engine.engine import SequenceStep
     eng = model.engine
@@ -281,7 +290,7 @@ def prefill_run(model, tokens, reps, layers, c=None, lens=None, breakdown=False)
     ms = statistics.median(times)
     out = {"ms": ms, "tok_s": sum(lens) / (ms / 1e3), "flops": prefill_flops(c or CONFIG_4B, layers, lens)}
     if breakdown:
-        out["breakdown"] = prefill_breakdown(eng, run_once)
+        out["breakdown"] = prefill_breakdown(eng, run_once, by_kernel)
     return out
 
 
@@ -327,6 +336,46 @@ def datasun_config(width, heads, kv, d, ff, layers):
                        for i in range(layers)]}
 
 
+BEPILORN_EXPERTS = 16          # experts of the routed feed-forward in the design runs; 4 are used, in 4 groups of which 2 are kept
+
+
+def bepilorn_config(width, heads, kv, d, ff, layers):
+    """A Bepilorn model of these layer sizes: every fourth layer the pair of chunked sink attention
+    and gated linear attention, the others state-space layers whose heads have the attention's
+    sizes; a routed feed-forward whose four used experts and shared expert together have the dense
+    feed-forward's inner size."""
+    ssm = {"heads": heads, "vdim": d, "state": d, "groups": kv, "conv": 4, "norm_groups": kv}
+    pair = {"left": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": DESIGN_WINDOW},
+                     "rot": {"base": 1e6, "dims": d // 2}},
+            "right": {"heads": heads, "dim": d, "vdim": d, "tau": 16.0, "rank": 64}, "left_scale": 0.6, "right_scale": 1.1}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff - 4 * (ff // 6)},
+           "router": {"experts": BEPILORN_EXPERTS, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Bepilorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.25,
+            "layers": [{"type": "parallel" if i % 4 == 3 else "mamba2", "mixer": pair if i % 4 == 3 else ssm, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def decode_breakdown(model, batch, ctx_len):
+    """One instrumented single-token step (no graph, an event around every kernel) behind prompts of
+    ``ctx_len`` tokens: milliseconds by kernel."""
+    import torch
+    from builderforce_inference_b200.engine.engine import SequenceStep
+    eng = model.engine
+    g = torch.Generator().manual_seed(7)
+    slots = [eng.acquire() for _ in range(batch)]
+    eng.step([SequenceStep(s, torch.randint(0, eng.spec.vocab_size, (ctx_len,), generator=g).tolist(), ()) for s in slots], check=False)
+    graphs, eng.use_graphs = eng.use_graphs, False
+    try:
+        def one():
+            eng.step([SequenceStep(s, (1,), (0,)) for s in slots], check=False)
+        one()
+        return prefill_breakdown(eng, one, by_kernel=True)
+    finally:
+        eng.use_graphs = graphs
+        for s in slots:
+            eng.release(s)
+
+
 def design_run(a) -> int:
     import torch
     from builderforce_inference_b200 import Model
@@ -337,23 +386,34 @@ def design_run(a) -> int:
     out = {}
     for name in (a.sizes.split(",") if a.sizes else sorted(DESIGN_SIZES)):
         width, heads, kv, d, ff = DESIGN_SIZES[name]
-        configs = {"datasun": datasun_config(width, heads, kv, d, ff, layers),
-                   "qwen3": dict(CONFIG_4B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
-                                 num_key_value_heads=kv, head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)}
+        qwen3 = dict(CONFIG_4B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                     num_key_value_heads=kv, head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
+        if a.design == "bepilorn":      # beside the closest design the package has, and beside the dense one
+            configs = {"bepilorn": bepilorn_config(width, heads, kv, d, ff, layers),
+                       "datasun": datasun_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
+        else:
+            configs = {"datasun": datasun_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
         for design, cfg in configs.items():
             model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2048, max_seq_len=CONTEXT, max_batch=64)
-            pf = prefill_run(model, PREFILL_TOKENS, 5, layers, breakdown=True)
+            by_kernel = a.design == "bepilorn"
+            pf = prefill_run(model, PREFILL_TOKENS, 5, layers, breakdown=True, by_kernel=by_kernel)
             row = {"prefill_2048": {"ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1), "breakdown": pf["breakdown"]}}
             for b in (8, 64):
                 decode_run(model, b, 2, 3, seed=3, lens=[1024] * b)
                 r = decode_run(model, b, 32, 3, seed=4, lens=[1024] * b)
                 row[f"decode_b{b}"] = {"tok_s": round(r["tok_s"], 1), "ms_per_step": round(r["ms_per_step"], 4),
                                        "weight_bytes": int(model.engine.decoder.n_weight_bytes), "launches_per_step": r["launches"] // 32}
+                if by_kernel:
+                    row[f"decode_b{b}"]["breakdown"] = decode_breakdown(model, b, 1024)
             out.setdefault(name, {})[design] = row
             del model
             torch.cuda.empty_cache()
-    print(json.dumps({"workloads": "datasun beside qwen3 at equal layer sizes, builder-run beside the benchmark", "dtype": "bf16",
-                      "layers": layers, "pattern": "lightning x3, attention (window %d) x1" % DESIGN_WINDOW, "vocab": DESIGN_VOCAB,
+    pattern = {"datasun": "lightning x3, attention (window %d) x1" % DESIGN_WINDOW,
+               "bepilorn": "state space x3, chunked attention (chunk %d) + gated linear attention x1; %d experts, 4 used, and a shared one"
+                           % (DESIGN_WINDOW, BEPILORN_EXPERTS)}[a.design]
+    print(json.dumps({"workloads": a.design + " beside " + ("datasun and qwen3" if a.design == "bepilorn" else "qwen3")
+                      + " at equal layer sizes, builder-run beside the benchmark", "dtype": "bf16",
+                      "layers": layers, "pattern": pattern, "vocab": DESIGN_VOCAB,
                       "peaks": pk["source"], "sizes": out, "clocks": clocks.stop()}))
     return 0
 
@@ -674,7 +734,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers of the same sizes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--design", default=None, choices=["datasun"],
+    ap.add_argument("--design", default=None, choices=["datasun", "bepilorn"],
                     help="instead of the benchmark: this design beside qwen3 at equal layer sizes (see design_run)")
     ap.add_argument("--sizes", default=None, help="with --design: names of DESIGN_SIZES, comma-separated (default: all)")
     a = ap.parse_args()

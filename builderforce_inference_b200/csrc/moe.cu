@@ -10,9 +10,16 @@
 //     a tie; the weights are the chosen experts' s (not renormalised) times `weight_scale`.
 //     With `extra` (a logit beside the experts', column E of z) gate[t] = sigmoid(z_E): the factor
 //     of an expert that every token uses.
+// bfi_moe_router: the same decision with the logits made here, z = W_router h (float32 rows of W).
 // bfi_moe_gate_up:  act[t, k, :] = silu(W_gate[e] h_t) * (W_up[e] h_t),  e = idx[t, k]
 // bfi_moe_down:     out[t, :] (= | +=) sum_k weight[t, k] * W_down[idx[t, k]] act[t, k, :]
 //                                      + gate[t] * shared[t, :]            (the last term optional)
+// The experts' weights are two matrices for all experts, the layouts the dense products take as well:
+// W_gu [E * 2 * ff, width], expert e's gate row j at row 2 (e ff + j) and its up row right after it;
+// W_down [width, E * ff], expert e's columns at e ff .. (e + 1) ff.
+// When most experts are used anyway (many tokens), the dense products compute every expert for every
+// token on the tensor cores and bfi_moe_weigh_dense multiplies the activations by the chosen experts'
+// weights (0 for the others) between the two products:  act[t, e ff + j] *= weight of e for token t.
 #include "common.cuh"
 
 __device__ __forceinline__ float moe_sigmoid(float x) {
@@ -21,20 +28,12 @@ __device__ __forceinline__ float moe_sigmoid(float x) {
     return z / (1.0f + z);
 }
 
-// One warp per token.  Shared memory per warp: s[E], choice[E], group[n_groups].
-__global__ void moe_route_kernel(const float* __restrict__ z, long z_stride, const float* __restrict__ correction,
-                                 int* __restrict__ idx, float* __restrict__ weight, float* __restrict__ gate,
-                                 int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra) {
-    pdl_trigger();
-    pdl_wait();
-    extern __shared__ float sm[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const int t = blockIdx.x * n_warps + warp;
-    if (t >= n_tokens) return;
-    float* s = sm + (size_t)warp * (2 * E + n_groups);
-    float* choice = s + E;
-    float* gs = choice + E;
-    const float* zr = z + (size_t)t * z_stride;
+// The decision of one token, by one warp: zr[0..E) are its logits (zr[E] the extra one), s, choice
+// (E floats each) and gs (n_groups floats) are the warp's scratch in shared memory.
+__device__ __forceinline__ void moe_route_token(const float* zr, const float* __restrict__ correction, int* __restrict__ idx,
+                                                float* __restrict__ weight, float* __restrict__ gate, float* s, float* choice,
+                                                float* gs, int t, int E, int top, int n_groups, int keep, float weight_scale,
+                                                int extra, int lane) {
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
     m = warp_max(m);
@@ -102,6 +101,21 @@ __global__ void moe_route_kernel(const float* __restrict__ z, long z_stride, con
     if (extra && lane == 0) gate[t] = moe_sigmoid(zr[E]);
 }
 
+// One warp per token, logits given.  Shared memory per warp: s[E], choice[E], group[n_groups].
+__global__ void moe_route_kernel(const float* __restrict__ z, long z_stride, const float* __restrict__ correction,
+                                 int* __restrict__ idx, float* __restrict__ weight, float* __restrict__ gate,
+                                 int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int t = blockIdx.x * n_warps + warp;
+    if (t >= n_tokens) return;
+    float* s = sm + (size_t)warp * (2 * E + n_groups);
+    moe_route_token(z + (size_t)t * z_stride, correction, idx, weight, gate, s, s + E, s + 2 * E, t, E, top, n_groups, keep,
+                    weight_scale, extra, lane);
+}
+
 extern "C" int bfi_moe_route(const float* z, long z_stride, const float* correction, int* idx, float* weight, float* gate,
                              int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra,
                              cudaStream_t stream) {
@@ -156,12 +170,70 @@ __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ w, cons
     return warp_sum(acc);
 }
 
+// The router's logits and its decision in one kernel: one block per token, the token's input as
+// float32 in shared memory, a warp per logit (router rows are float32 [E (+1), width]), then warp 0
+// decides.  The logits are float32 sums of float32 products of the input as its storage type holds it.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ w_router,
+                  const float* __restrict__ correction, const int* __restrict__ token_slot, int* __restrict__ idx,
+                  float* __restrict__ weight, float* __restrict__ gate, int width, int E, int top, int n_groups, int keep,
+                  float weight_scale, int extra) {
+    pdl_trigger();
+    extern __shared__ float sm[];
+    float* hs = sm;                                // [width]
+    float* z = hs + width;                         // [E + 1]
+    float* scratch = z + E + 1;                    // [2 E + n_groups]
+    const int t = blockIdx.x;
+    if (token_slot[t] < 0) return;
+    pdl_wait();
+    for (int j = threadIdx.x; j < width; j += blockDim.x) hs[j] = to_f32(h[(size_t)t * h_stride + j]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E + (extra ? 1 : 0); e += n_warps) {
+        const float d = warp_dot<float>(w_router + (size_t)e * width, hs, width, lane);
+        if (lane == 0) z[e] = d;
+    }
+    __syncthreads();
+    if (warp == 0)
+        moe_route_token(z, correction, idx, weight, gate, scratch, scratch + E, scratch + 2 * E, t, E, top, n_groups, keep,
+                        weight_scale, extra, lane);
+}
+
+extern "C" int bfi_moe_router(const void* h, long h_stride, int dtype, const float* w_router, const float* correction,
+                              const int* token_slot, int* idx, float* weight, float* gate, int n_tokens, int width, int E,
+                              int top, int n_groups, int keep, float weight_scale, int extra, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype), "moe_router: unknown dtype code %d", dtype);
+    BFI_REQUIRE(E > 0 && top > 0 && top <= E && width > 0 && h_stride >= width, "moe_router: cannot choose %d of %d experts", top, E);
+    BFI_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups,
+                "moe_router: %d experts in %d groups, %d kept", E, n_groups, keep);
+    BFI_REQUIRE((long)keep * (E / n_groups) >= top, "moe_router: %d groups of %d experts cannot give %d", keep, E / n_groups, top);
+    BFI_REQUIRE(!extra || gate != nullptr, "moe_router: the extra logit needs a place for its gate");
+    if (n_tokens <= 0) return 0;
+    const size_t smem = (size_t)(width + 3 * E + 1 + n_groups) * sizeof(float);
+    BFI_REQUIRE(smem <= 160 * 1024, "moe_router: width %d and %d experts do not fit shared memory", width, E);
+    cudaError_t e = cudaSuccess;
+    if (dtype == BFI_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            bfi_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)h, h_stride, w_router, correction,
+                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            bfi_launch(moe_router_kernel<bf16>, dim3(n_tokens), dim3(128), smem, stream, (const bf16*)h, h_stride, w_router, correction,
+                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
+    }
+    if (e != cudaSuccess) return bfi_fail("moe_router: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    return bfi_check_launch("moe_router");
+}
+
 #define MOE_WARPS 8
 
-// grid (pairs, chunks of ff rows); W_gate, W_up: [E][ff][width]
+// grid (pairs, chunks of ff rows)
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
-moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ w_gate, const T* __restrict__ w_up,
+moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ w_gu,
                    const int* __restrict__ idx, const int* __restrict__ token_slot, T* __restrict__ act, int top,
                    int width, int ff, int rows_per_block) {
     pdl_trigger();
@@ -177,14 +249,14 @@ moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__
     const int r0 = blockIdx.y * rows_per_block;
     const int r1 = min(ff, r0 + rows_per_block);
     for (int r = r0 + warp; r < r1; r += MOE_WARPS) {
-        const size_t off = ((size_t)e * ff + r) * width;
-        const float g = warp_dot<T>(w_gate + off, hs, width, lane);
-        const float u = warp_dot<T>(w_up + off, hs, width, lane);
+        const size_t off = ((size_t)e * ff + r) * 2 * width;
+        const float g = warp_dot<T>(w_gu + off, hs, width, lane);
+        const float u = warp_dot<T>(w_gu + off + width, hs, width, lane);
         if (lane == 0) act[(size_t)pair * ff + r] = from_f32<T>(g * moe_sigmoid(g) * u);
     }
 }
 
-extern "C" int bfi_moe_gate_up(const void* h, long h_stride, int dtype, const void* w_gate, const void* w_up,
+extern "C" int bfi_moe_gate_up(const void* h, long h_stride, int dtype, const void* w_gu,
                                const int* idx, const int* token_slot, void* act, int n_tokens, int top, int width, int ff,
                                cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_gate_up: unknown dtype code %d", dtype);
@@ -206,24 +278,24 @@ extern "C" int bfi_moe_gate_up(const void* h, long h_stride, int dtype, const vo
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_gate_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_gate_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)h, h_stride,
-                       (const float*)w_gate, (const float*)w_up, idx, token_slot, (float*)act, top, width, ff, rows_per_block);
+                       (const float*)w_gu, idx, token_slot, (float*)act, top, width, ff, rows_per_block);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_gate_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_gate_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, h_stride,
-                       (const bf16*)w_gate, (const bf16*)w_up, idx, token_slot, (bf16*)act, top, width, ff, rows_per_block);
+                       (const bf16*)w_gu, idx, token_slot, (bf16*)act, top, width, ff, rows_per_block);
     }
     if (e != cudaSuccess) return bfi_fail("moe_gate_up: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     return bfi_check_launch("moe_gate_up");
 }
 
-// grid (tokens, chunks of output columns); W_down: [E][width][ff]
+// grid (tokens, chunks of output columns)
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ idx,
                 const float* __restrict__ weight, const int* __restrict__ token_slot, const float* __restrict__ shared_out,
                 long shared_stride, const float* __restrict__ gate, float* __restrict__ out, long out_stride, int top,
-                int width, int ff, int cols_per_block, int accumulate) {
+                int width, int ff, int n_experts, int cols_per_block, int accumulate) {
     pdl_trigger();
     extern __shared__ float as[];                  // [top][ff]
     const int t = blockIdx.x;
@@ -239,7 +311,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
         float sum = 0.0f;
         for (int k = 0; k < top; ++k) {
             const int e = idx[(size_t)t * top + k];
-            const float d = warp_dot<T>(w_down + ((size_t)e * width + c) * ff, as + (size_t)k * ff, ff, lane);
+            const float d = warp_dot<T>(w_down + (size_t)c * n_experts * ff + (size_t)e * ff, as + (size_t)k * ff, ff, lane);
             sum = fmaf(weight[(size_t)t * top + k], d, sum);
         }
         if (lane == 0) {
@@ -252,8 +324,8 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
 
 extern "C" int bfi_moe_down(const void* act, int dtype, const void* w_down, const int* idx, const float* weight,
                             const int* token_slot, const float* shared_out, long shared_stride, const float* gate,
-                            float* out, long out_stride, int n_tokens, int top, int width, int ff, int accumulate,
-                            cudaStream_t stream) {
+                            float* out, long out_stride, int n_tokens, int top, int width, int ff, int n_experts,
+                            int accumulate, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_down: unknown dtype code %d", dtype);
     BFI_REQUIRE(top > 0 && width > 0 && ff > 0 && out_stride >= width, "moe_down: bad sizes");
     BFI_REQUIRE(!shared_out || shared_stride >= width, "moe_down: the shared output's rows are shorter than the width");
@@ -271,15 +343,55 @@ extern "C" int bfi_moe_down(const void* act, int dtype, const void* w_down, cons
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_down_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)act, (const float*)w_down, idx,
-                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, cols_per_block, accumulate);
+                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, n_experts, cols_per_block,
+                       accumulate);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_down_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)act, (const bf16*)w_down, idx,
-                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, cols_per_block, accumulate);
+                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, n_experts, cols_per_block,
+                       accumulate);
     }
     if (e != cudaSuccess) return bfi_fail("moe_down: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     return bfi_check_launch("moe_down");
+}
+
+// one block per token; act [tokens][E * ff]
+template <typename T>
+__global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, const int* __restrict__ idx,
+                                       const float* __restrict__ weight, const int* __restrict__ token_slot, int top, int E,
+                                       int ff) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float comb[];                // [E] the token's weight of every expert
+    const int t = blockIdx.x;
+    if (token_slot[t] < 0) return;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) comb[e] = 0.0f;
+    __syncthreads();
+    if (threadIdx.x < top) comb[idx[(size_t)t * top + threadIdx.x]] = weight[(size_t)t * top + threadIdx.x];
+    __syncthreads();
+    T* row = act + (size_t)t * act_stride;
+    for (int j = threadIdx.x; j < E * ff; j += blockDim.x) {
+        const float c = comb[j / ff];
+        row[j] = c == 0.0f ? from_f32<T>(0.0f) : from_f32<T>(to_f32(row[j]) * c);
+    }
+}
+
+extern "C" int bfi_moe_weigh_dense(void* act, long act_stride, int dtype, const int* idx, const float* weight,
+                                   const int* token_slot, int n_tokens, int top, int E, int ff, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype), "moe_weigh_dense: unknown dtype code %d", dtype);
+    BFI_REQUIRE(top > 0 && top <= 1024 && E > 0 && ff > 0 && act_stride >= (long)E * ff, "moe_weigh_dense: bad sizes");
+    if (n_tokens <= 0) return 0;
+    const size_t smem = (size_t)E * sizeof(float);
+    BFI_REQUIRE(smem <= 48 * 1024, "moe_weigh_dense: %d experts are too many for this kernel", E);
+    const int threads = top > 256 ? 1024 : 256;
+    if (dtype == BFI_F32)
+        bfi_launch(moe_weigh_dense_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (float*)act, act_stride, idx, weight,
+                   token_slot, top, E, ff);
+    else
+        bfi_launch(moe_weigh_dense_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, stream, (bf16*)act, act_stride, idx, weight,
+                   token_slot, top, E, ff);
+    return bfi_check_launch("moe_weigh_dense");
 }
 
 BFI_TRACE_EXPORT(moe)

@@ -40,12 +40,23 @@ struct RecArgs {
     float q_scale, inv_tau;
     const float *bias, *rate, *skip;                   // float32: [H] or [H*D] bias, [H] rate, [H] skip (or null)
     const int *cu_seqlens, *seq_slot;
-    int vb, v_blocks;
+    int vb, v_blocks, chunk_len;
 };
 
-template <typename T>
+// PHASE 0: a sequence's new tokens in order, from the slot's state, which is moved on.
+// The other phases cut every sequence into chunks of `chunk_len` tokens that run side by side
+// (blockIdx.z is the chunk; chunk c of sequence s has the running number base(s) + c, where base
+// counts the chunks of the sequences before s):
+// PHASE 1: a chunk alone from a zero state: out gets the part of o that the chunk's own tokens give,
+//          chunk_state[n] the state the chunk adds (sum_j diag(prod_{i>j} a_i) k_j (c_j v_j)^T) and
+//          chunk_decay[n] the product of the chunk's decays per row.
+// (between them decay_chunk_carry_kernel walks the chunks of a sequence in order and leaves in
+//  chunk_state[n] the state that chunk n starts from, and in the slot's state the one after the last)
+// PHASE 3: out += (q_t * prod_{i<=t in chunk} a_i)^T chunk_state[n]: what the tokens before the chunk give.
+template <typename T, int PHASE>
 __global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, const T* __restrict__ raw,
-                                  float* __restrict__ out, float* __restrict__ state, const RecArgs a) {
+                                  float* __restrict__ out, float* __restrict__ state, float* __restrict__ chunk_state,
+                                  float* __restrict__ chunk_decay, const RecArgs a) {
     pdl_trigger();
     extern __shared__ float sm[];
     const int D = a.D, V = a.V, vb = a.vb;
@@ -53,22 +64,40 @@ __global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict_
     float* qs = S + (size_t)D * vb;     // [D]
     float* ks = qs + D;                 // [D]
     float* as = ks + D;                 // [D] decay per row
-    float* red = as + D;                // [threads]
+    float* ps = as + D;                 // [D] product of the chunk's decays so far per row
+    float* red = ps + D;                // [threads]
     __shared__ float step_c;
     const int seq = blockIdx.y;
     const int slot = a.seq_slot[seq];
     if (slot < 0) return;
     const int h = blockIdx.x / a.v_blocks;
     const int v0 = (blockIdx.x - h * a.v_blocks) * vb;
-    const int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
+    int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
+    size_t chunk_no = 0;
+    if (PHASE != 0) {
+        const int first = blockIdx.z * a.chunk_len;
+        if (first >= nt) return;
+        for (int s2 = 0; s2 < seq; ++s2)
+            chunk_no += (a.cu_seqlens[s2 + 1] - a.cu_seqlens[s2] + a.chunk_len - 1) / a.chunk_len;
+        chunk_no += blockIdx.z;
+        t0 += first;
+        nt = min(a.chunk_len, nt - first);
+    }
     const int c = threadIdx.x % vb, g = threadIdx.x / vb, ng = blockDim.x / vb;
     const bool col_ok = v0 + c < V;
     const int grp = h / a.heads_per_group;
     const float skip = a.skip ? a.skip[h] : 0.0f;
     // the state of earlier steps (zeroed when the slot was taken) does not come from this step's kernels
-    float* sp = state + (((size_t)slot * a.H + h) * D) * V + v0;
-    for (int d = g; d < D; d += ng) S[d * vb + c] = col_ok ? sp[(size_t)d * V + c] : 0.0f;
-    pdl_wait();
+    float* sp = PHASE == 0 ? state + (((size_t)slot * a.H + h) * D) * V + v0
+                           : chunk_state + ((chunk_no * a.H + h) * D) * V + v0;
+    if (PHASE == 0) {
+        for (int d = g; d < D; d += ng) S[d * vb + c] = col_ok ? sp[(size_t)d * V + c] : 0.0f;
+        pdl_wait();
+    } else {
+        pdl_wait();
+        for (int d = g; d < D; d += ng) S[d * vb + c] = (PHASE == 3 && col_ok) ? sp[(size_t)d * V + c] : 0.0f;
+        for (int j = threadIdx.x; j < D; j += blockDim.x) ps[j] = 1.0f;
+    }
     for (int t = 0; t < nt; ++t) {
         const size_t tok = (size_t)(t0 + t);
         const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
@@ -79,45 +108,303 @@ __global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict_
             const float w = expf(-a.rate[h] * step_c);
             for (int j = threadIdx.x; j < D; j += blockDim.x) {
                 qs[j] = to_f32(row[a.q_off + j]) * a.q_scale;
-                ks[j] = to_f32(row[a.k_off + j]);
+                if (PHASE != 3) ks[j] = to_f32(row[a.k_off + j]);
                 as[j] = w;
+                if (PHASE != 0) ps[j] *= w;
             }
         } else {
             if (threadIdx.x == 0) step_c = 1.0f;
             for (int j = threadIdx.x; j < D; j += blockDim.x) {
                 qs[j] = to_f32(row[a.q_off + j]) * a.q_scale;
-                ks[j] = to_f32(row[a.k_off + j]);
-                as[j] = expf(rec_log_sigmoid(to_f32(rr[(size_t)h * D + j]) + a.bias[(size_t)h * D + j]) * a.inv_tau);
+                if (PHASE != 3) ks[j] = to_f32(row[a.k_off + j]);
+                const float w = expf(rec_log_sigmoid(to_f32(rr[(size_t)h * D + j]) + a.bias[(size_t)h * D + j]) * a.inv_tau);
+                as[j] = w;
+                if (PHASE != 0) ps[j] *= w;
             }
         }
         float vv = 0.0f;
-        if (col_ok) vv = to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + v0 + c]);
+        if (PHASE != 3 && col_ok) vv = to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + v0 + c]);
         __syncthreads();
-        const float cv = step_c * vv;
         float acc = 0.0f;
-        for (int d = g; d < D; d += ng) {
-            const float s = fmaf(as[d], S[d * vb + c], ks[d] * cv);
-            S[d * vb + c] = s;
-            acc = fmaf(s, qs[d], acc);
+        if (PHASE == 3) {
+            for (int d = g; d < D; d += ng) acc = fmaf(S[d * vb + c], qs[d] * ps[d], acc);
+        } else {
+            const float cv = step_c * vv;
+            for (int d = g; d < D; d += ng) {
+                const float s = fmaf(as[d], S[d * vb + c], ks[d] * cv);
+                S[d * vb + c] = s;
+                acc = fmaf(s, qs[d], acc);
+            }
         }
         red[threadIdx.x] = acc;
         __syncthreads();
         if (threadIdx.x < vb && col_ok) {
             float o = 0.0f;
             for (int i = 0; i < ng; ++i) o += red[i * vb + threadIdx.x];
-            out[tok * a.out_stride + (size_t)h * V + v0 + c] = fmaf(skip, vv, o);
+            float* dst = out + tok * a.out_stride + (size_t)h * V + v0 + c;
+            if (PHASE == 3) *dst += o;
+            else *dst = fmaf(skip, vv, o);
         }
     }
-    if (col_ok)
+    if (PHASE != 3 && col_ok)
         for (int d = g; d < D; d += ng) sp[(size_t)d * V + c] = S[d * vb + c];
+    if (PHASE == 1 && v0 == 0)
+        for (int j = threadIdx.x; j < D; j += blockDim.x) chunk_decay[(chunk_no * a.H + h) * D + j] = ps[j];
 }
 
+// The same three phases with the state in registers, for D up to 128: a warp owns 32 columns of one
+// head of one sequence (or chunk), lane l holds all D rows of column v0 + l, so a token's output
+// value is one thread's sum and the warp never waits for another.  The lanes share the work of
+// fetching the token's q, k and decay input (lane l fetches rows l, l + 32, ..., one token ahead of
+// the arithmetic) and of evaluating the decay, and pass them to each other through the warp's own
+// piece of shared memory.
+#define REC_WARPS 4
+
+template <typename T, int PHASE, int MODE, int DMAX>
+__global__ void __launch_bounds__(REC_WARPS * 32)
+decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, const T* __restrict__ raw,
+                       float* __restrict__ out, float* __restrict__ state, float* __restrict__ chunk_state,
+                       float* __restrict__ chunk_decay, const RecArgs a) {
+    pdl_trigger();
+    constexpr int R = DMAX / 32;                   // rows a lane fetches
+    __shared__ __align__(16) float stage[REC_WARPS][3][DMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int unit = blockIdx.x * REC_WARPS + warp;
+    const int seq = blockIdx.y;
+    const int slot = a.seq_slot[seq];
+    if (slot < 0 || unit >= a.H * a.v_blocks) return;
+    const int D = a.D, V = a.V;
+    const int h = unit / a.v_blocks;
+    const int col = (unit - h * a.v_blocks) * 32 + lane;
+    const bool col_ok = col < V;
+    int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
+    size_t chunk_no = 0;
+    if (PHASE != 0) {
+        const int first = blockIdx.z * a.chunk_len;
+        if (first >= nt) return;
+        for (int s2 = 0; s2 < seq; ++s2)
+            chunk_no += (a.cu_seqlens[s2 + 1] - a.cu_seqlens[s2] + a.chunk_len - 1) / a.chunk_len;
+        chunk_no += blockIdx.z;
+        t0 += first;
+        nt = min(a.chunk_len, nt - first);
+    }
+    const int grp = h / a.heads_per_group;
+    const float skip = a.skip ? a.skip[h] : 0.0f;
+    float* qs = stage[warp][0];
+    float* ks = stage[warp][1];
+    float* as = stage[warp][2];
+    float* sp = PHASE == 0 ? state + (((size_t)slot * a.H + h) * D) * V + col
+                           : chunk_state + ((chunk_no * a.H + h) * D) * V + col;
+    float S[DMAX];
+    if (PHASE == 0) {
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d) S[d] = (col_ok && d < D) ? sp[(size_t)d * V] : 0.0f;
+        pdl_wait();
+    } else {
+        pdl_wait();
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d) S[d] = (PHASE == 3 && col_ok && d < D) ? sp[(size_t)d * V] : 0.0f;
+    }
+    // the decay's constants of this lane's rows, and the running product of the chunk's decays
+    float bias_r[R], prod[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int d = lane + 32 * i;
+        bias_r[i] = (MODE == REC_DECAY_SIGMOID && d < D) ? a.bias[(size_t)h * D + d] : 0.0f;
+        prod[i] = 1.0f;
+    }
+    const float bias_h = MODE == REC_DECAY_STEP ? a.bias[h] : 0.0f;
+    const float rate_h = MODE == REC_DECAY_STEP ? a.rate[h] : 0.0f;
+    // the first token's inputs
+    float nq[R], nk[R], nr[R], nv = 0.0f, nstep = 0.0f;
+    auto fetch = [&](int t) {
+        const size_t tok = (size_t)(t0 + t);
+        const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
+        const T* rr = raw + tok * a.r_stride + a.r_off;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int d = lane + 32 * i;
+            nq[i] = d < D ? to_f32(row[a.q_off + d]) : 0.0f;
+            nk[i] = (PHASE != 3 && d < D) ? to_f32(row[a.k_off + d]) : 0.0f;
+            nr[i] = (MODE == REC_DECAY_SIGMOID && d < D) ? to_f32(rr[(size_t)h * D + d]) : 0.0f;
+        }
+        if (MODE == REC_DECAY_STEP) nstep = to_f32(rr[h]);
+        nv = (PHASE != 3 && col_ok) ? to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + col]) : 0.0f;
+    };
+    if (nt > 0) fetch(0);
+    for (int t = 0; t < nt; ++t) {
+        float step_c = 1.0f, w_h = 1.0f;
+        if (MODE == REC_DECAY_STEP) {
+            step_c = rec_softplus(nstep + bias_h);
+            w_h = expf(-rate_h * step_c);
+        }
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int d = lane + 32 * i;
+            float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(nr[i] + bias_r[i]) * a.inv_tau);
+            if (d >= D) w = 1.0f;
+            if (PHASE != 0) prod[i] *= w;
+            qs[d] = nq[i] * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f);
+            ks[d] = nk[i];
+            as[d] = w;
+        }
+        const float vv = nv;
+        __syncwarp();
+        if (t + 1 < nt) fetch(t + 1);
+        const float cv = step_c * vv;
+        float acc = 0.0f;
+#pragma unroll
+        for (int d4 = 0; d4 < DMAX; d4 += 4) {
+            if (d4 < D) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + d4);
+                if (PHASE == 3) {
+                    acc = fmaf(S[d4], q4.x, acc), acc = fmaf(S[d4 + 1], q4.y, acc);
+                    acc = fmaf(S[d4 + 2], q4.z, acc), acc = fmaf(S[d4 + 3], q4.w, acc);
+                } else {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + d4);
+                    float4 a4;
+                    if (MODE == REC_DECAY_STEP) a4 = make_float4(w_h, w_h, w_h, w_h);
+                    else a4 = *reinterpret_cast<const float4*>(as + d4);
+                    S[d4] = fmaf(a4.x, S[d4], k4.x * cv), acc = fmaf(S[d4], q4.x, acc);
+                    S[d4 + 1] = fmaf(a4.y, S[d4 + 1], k4.y * cv), acc = fmaf(S[d4 + 1], q4.y, acc);
+                    S[d4 + 2] = fmaf(a4.z, S[d4 + 2], k4.z * cv), acc = fmaf(S[d4 + 2], q4.z, acc);
+                    S[d4 + 3] = fmaf(a4.w, S[d4 + 3], k4.w * cv), acc = fmaf(S[d4 + 3], q4.w, acc);
+                }
+            }
+        }
+        if (col_ok) {
+            float* dst = out + (size_t)(t0 + t) * a.out_stride + (size_t)h * V + col;
+            if (PHASE == 3) *dst += acc;
+            else *dst = fmaf(skip, vv, acc);
+        }
+        __syncwarp();
+    }
+    if (PHASE != 3 && col_ok) {
+#pragma unroll
+        for (int d = 0; d < DMAX; ++d)
+            if (d < D) sp[(size_t)d * V] = S[d];
+    }
+    if (PHASE == 1 && unit == h * a.v_blocks) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) chunk_decay[(chunk_no * a.H + h) * D + d] = prod[i];
+        }
+    }
+}
+
+// One thread per element of a head's state: S = state[slot]; for every chunk of the sequence in
+// order: the chunk's place receives S (the state it starts from) and S = decay_row * S + what the
+// chunk adds; at the end state[slot] = S.
+__global__ void decay_chunk_carry_kernel(float* __restrict__ state, float* __restrict__ chunk_state,
+                                         const float* __restrict__ chunk_decay, const int* __restrict__ cu_seqlens,
+                                         const int* __restrict__ seq_slot, int H, int D, int V, int chunk_len) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.z, h = blockIdx.y;
+    const int slot = seq_slot[seq];
+    if (slot < 0) return;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= D * V) return;
+    const int d = e / V;
+    size_t base = 0;
+    for (int s2 = 0; s2 < seq; ++s2) base += (cu_seqlens[s2 + 1] - cu_seqlens[s2] + chunk_len - 1) / chunk_len;
+    const int n_chunks = (cu_seqlens[seq + 1] - cu_seqlens[seq] + chunk_len - 1) / chunk_len;
+    float* sp = state + ((size_t)slot * H + h) * D * V + e;
+    float S = *sp;
+    for (int cnk = 0; cnk < n_chunks; ++cnk) {
+        float* cs = chunk_state + ((base + cnk) * H + h) * D * V + e;
+        const float add = *cs;
+        *cs = S;
+        S = fmaf(chunk_decay[((base + cnk) * H + h) * D + d], S, add);
+    }
+    *sp = S;
+}
+
+template <typename T>
+static int launch_decay_scan(const void* qk, const void* vsrc, const void* raw, float* out, float* state, float* chunk_state,
+                             float* chunk_decay, RecArgs a, int n_seqs, int threads, size_t smem, int max_chunks,
+                             cudaStream_t stream) {
+    const dim3 grid(a.H * a.v_blocks, n_seqs, max_chunks > 0 ? max_chunks : 1), block(threads);
+    cudaError_t e = cudaSuccess;
+#define BFI_REC_LAUNCH(PH)                                                                                               \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(decay_scan_kernel<T, PH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess)                                                                                            \
+            bfi_launch(decay_scan_kernel<T, PH>, grid, block, smem, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out, state,     \
+                       chunk_state, chunk_decay, a);                                                                     \
+    } while (0)
+    if (max_chunks <= 0) {
+        BFI_REC_LAUNCH(0);
+    } else {
+        BFI_REC_LAUNCH(1);
+        if (e == cudaSuccess) {
+            const int per = a.D * a.V;
+            bfi_launch(decay_chunk_carry_kernel, dim3((per + 255) / 256, a.H, n_seqs), dim3(256), 0, stream, state, chunk_state,
+                       (const float*)chunk_decay, a.cu_seqlens, a.seq_slot, a.H, a.D, a.V, a.chunk_len);
+            BFI_REC_LAUNCH(3);
+        }
+    }
+#undef BFI_REC_LAUNCH
+    if (e != cudaSuccess) return bfi_fail("decay_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    return bfi_check_launch("decay_scan");
+}
+
+template <typename T, int MODE, int DMAX>
+static void launch_regs_phases(const void* qk, const void* vsrc, const void* raw, float* out, float* state, float* chunk_state,
+                               float* chunk_decay, const RecArgs& a, int n_seqs, int max_chunks, cudaStream_t stream) {
+    const dim3 grid((a.H * a.v_blocks + REC_WARPS - 1) / REC_WARPS, n_seqs, max_chunks > 0 ? max_chunks : 1), block(REC_WARPS * 32);
+    if (max_chunks <= 0) {
+        bfi_launch(decay_scan_regs_kernel<T, 0, MODE, DMAX>, grid, block, 0, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out,
+                   state, chunk_state, chunk_decay, a);
+        return;
+    }
+    bfi_launch(decay_scan_regs_kernel<T, 1, MODE, DMAX>, grid, block, 0, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out,
+               state, chunk_state, chunk_decay, a);
+    const int per = a.D * a.V;
+    bfi_launch(decay_chunk_carry_kernel, dim3((per + 255) / 256, a.H, n_seqs), dim3(256), 0, stream, state, chunk_state,
+               (const float*)chunk_decay, a.cu_seqlens, a.seq_slot, a.H, a.D, a.V, a.chunk_len);
+    bfi_launch(decay_scan_regs_kernel<T, 3, MODE, DMAX>, grid, block, 0, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out,
+               state, chunk_state, chunk_decay, a);
+}
+
+template <typename T>
+static int launch_decay_scan_regs(const void* qk, const void* vsrc, const void* raw, float* out, float* state,
+                                  float* chunk_state, float* chunk_decay, RecArgs a, int n_seqs, int max_chunks,
+                                  cudaStream_t stream) {
+    a.vb = 32, a.v_blocks = (a.V + 31) / 32;
+#define BFI_REC_REGS(M, DM) \
+    launch_regs_phases<T, M, DM>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, max_chunks, stream)
+    if (a.mode == REC_DECAY_STEP) {
+        if (a.D <= 32) BFI_REC_REGS(REC_DECAY_STEP, 32);
+        else if (a.D <= 64) BFI_REC_REGS(REC_DECAY_STEP, 64);
+        else BFI_REC_REGS(REC_DECAY_STEP, 128);
+    } else {
+        if (a.D <= 32) BFI_REC_REGS(REC_DECAY_SIGMOID, 32);
+        else if (a.D <= 64) BFI_REC_REGS(REC_DECAY_SIGMOID, 64);
+        else BFI_REC_REGS(REC_DECAY_SIGMOID, 128);
+    }
+#undef BFI_REC_REGS
+    return bfi_check_launch("decay_scan");
+}
+
+// Tests set this to run the general kernels (the state in shared memory) at sizes the register
+// kernels would take.
+static int g_rec_general = 0;
+extern "C" int bfi_decay_scan_general(int on) {
+    g_rec_general = on ? 1 : 0;
+    return 0;
+}
+
+// `chunk_len` > 0 runs the chunked form: `chunk_state` then holds H * D * V floats and `chunk_decay`
+// H * D floats for every chunk of the step (sum over the sequences of ceil(tokens / chunk_len), at
+// most n_tokens / chunk_len + n_seqs), and `max_chunks` is the most chunks one sequence has.
 extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_off, const void* vsrc, long v_stride,
                               int v_off, const void* raw, long r_stride, int r_off, int dtype, float* out,
                               long out_stride, float* state, const int* cu_seqlens, const int* seq_slot, int n_seqs,
                               int H, int D, int V, int heads_per_group, int mode, float q_scale, float inv_tau,
-                              const float* bias, const float* rate, const float* skip, int few_tokens,
-                              cudaStream_t stream) {
+                              const float* bias, const float* rate, const float* skip, int few_tokens, int chunk_len,
+                              int max_chunks, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "decay_scan: unknown dtype code %d", dtype);
     BFI_REQUIRE(H > 0 && D > 0 && V > 0, "decay_scan: bad sizes heads=%d dim=%d vdim=%d", H, D, V);
     BFI_REQUIRE(heads_per_group > 0 && H % heads_per_group == 0, "decay_scan: %d heads do not form groups of %d", H,
@@ -125,13 +412,22 @@ extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_o
     BFI_REQUIRE(mode == REC_DECAY_STEP || mode == REC_DECAY_SIGMOID, "decay_scan: unknown decay form %d", mode);
     BFI_REQUIRE(bias != nullptr && (mode != REC_DECAY_STEP || rate != nullptr), "decay_scan: the decay's constants are missing");
     BFI_REQUIRE(out_stride >= (long)H * V, "decay_scan: output stride shorter than the heads");
+    BFI_REQUIRE(chunk_len == 0 || (chunk_len > 0 && max_chunks > 0 && max_chunks <= 65535 && chunk_state && chunk_decay),
+                "decay_scan: the chunked form needs its chunk length, count and scratch");
     if (n_seqs <= 0) return 0;
     RecArgs a;
     a.qk_stride = qk_stride, a.v_stride = v_stride, a.r_stride = r_stride, a.out_stride = out_stride;
     a.q_off = q_off, a.k_off = k_off, a.v_off = v_off, a.r_off = r_off;
     a.H = H, a.D = D, a.V = V, a.heads_per_group = heads_per_group, a.mode = mode;
     a.q_scale = q_scale, a.inv_tau = inv_tau, a.bias = bias, a.rate = rate, a.skip = skip;
-    a.cu_seqlens = cu_seqlens, a.seq_slot = seq_slot;
+    a.cu_seqlens = cu_seqlens, a.seq_slot = seq_slot, a.chunk_len = chunk_len;
+    if (D <= 128 && !g_rec_general && (long)H * ((V + 31) / 32) <= 2147483647L && n_seqs <= 65535) {
+        // the state in registers, a warp per 32 columns
+        const int chunks_r = chunk_len > 0 ? max_chunks : 0;
+        if (dtype == BFI_F32)
+            return launch_decay_scan_regs<float>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, chunks_r, stream);
+        return launch_decay_scan_regs<bf16>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, chunks_r, stream);
+    }
     // columns per block: few where the step is short (more blocks share the state's traffic)
     int vb = V;
     const int want = few_tokens ? 16 : 32;
@@ -141,22 +437,12 @@ extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_o
     if (threads < 32) threads = vb * ((32 + vb - 1) / vb);
     a.vb = vb, a.v_blocks = v_blocks;
     BFI_REQUIRE((long)H * v_blocks <= 2147483647L && n_seqs <= 65535, "decay_scan: too many heads or sequences for one launch");
-    const size_t smem = ((size_t)D * vb + 3 * (size_t)D + threads) * sizeof(float);
+    const size_t smem = ((size_t)D * vb + 4 * (size_t)D + threads) * sizeof(float);
     BFI_REQUIRE(smem <= 200 * 1024, "decay_scan: a state tile of %d x %d does not fit shared memory", D, vb);
-    cudaError_t e = cudaSuccess;
-    if (dtype == BFI_F32) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(decay_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-            bfi_launch(decay_scan_kernel<float>, dim3(H * v_blocks, n_seqs), dim3(threads), smem, stream, (const float*)qk,
-                       (const float*)vsrc, (const float*)raw, out, state, a);
-    } else {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(decay_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess)
-            bfi_launch(decay_scan_kernel<bf16>, dim3(H * v_blocks, n_seqs), dim3(threads), smem, stream, (const bf16*)qk,
-                       (const bf16*)vsrc, (const bf16*)raw, out, state, a);
-    }
-    if (e != cudaSuccess) return bfi_fail("decay_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    return bfi_check_launch("decay_scan");
+    const int chunks = chunk_len > 0 ? max_chunks : 0;
+    if (dtype == BFI_F32)
+        return launch_decay_scan<float>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, threads, smem, chunks, stream);
+    return launch_decay_scan<bf16>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, threads, smem, chunks, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -4,6 +4,7 @@
 //   bfi_norm_add:      x[t, :] += y[t, :] * rsqrt(mean(y[t, :]^2) + eps) * w        (y float32)
 //   bfi_weighted_sum:  out[t, :] = a * y0[t, :] + b * y1[t, :]                      (all float32)
 //   bfi_scale_rows:    x[r, :] *= s                                                 (float32)
+//   bfi_gated_rows:    out[r, :] (= | +=) g[r] * src[r, :]                          (float32)
 //
 // The residual stream x and the sublayer outputs are float32 in every run dtype; the weight is
 // float32 or bfloat16.  All arithmetic is float32.
@@ -66,6 +67,29 @@ extern "C" int bfi_scale_rows(float* x, long stride, int n_rows, int cols, float
     BFI_REQUIRE(n_rows <= 65535, "scale_rows: %d rows are too many for one launch", n_rows);
     bfi_launch(scale_rows_kernel, dim3((cols + 255) / 256, n_rows), dim3(256), 0, stream, x, stride, cols, s);
     return bfi_check_launch("scale_rows");
+}
+
+__global__ void gated_rows_kernel(float* __restrict__ out, long out_stride, const float* __restrict__ src, long src_stride,
+                                  const float* __restrict__ g, int cols, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    float* o = out + (size_t)r * out_stride + j;
+    const float v = g[r] * src[(size_t)r * src_stride + j];
+    *o = accumulate ? *o + v : v;
+}
+
+// out[r, :] (= | +=) g[r] * src[r, :] over float32 rows (a sublayer's part with one factor per token)
+extern "C" int bfi_gated_rows(float* out, long out_stride, const float* src, long src_stride, const float* g, int n_rows,
+                              int cols, int accumulate, cudaStream_t stream) {
+    BFI_REQUIRE(n_rows >= 0 && cols > 0 && out_stride >= cols && src_stride >= cols, "gated_rows: bad sizes rows=%d cols=%d", n_rows, cols);
+    if (n_rows == 0) return 0;
+    BFI_REQUIRE(n_rows <= 65535, "gated_rows: %d rows are too many for one launch", n_rows);
+    bfi_launch(gated_rows_kernel, dim3((cols + 255) / 256, n_rows), dim3(256), 0, stream, out, out_stride, src, src_stride, g, cols,
+               accumulate);
+    return bfi_check_launch("gated_rows");
 }
 
 BFI_TRACE_EXPORT(sublayer_out)

@@ -371,6 +371,18 @@ def scale_rows(x: torch.Tensor, s: float) -> None:
                          c_float(s), _stream())
 
 
+def gated_rows(out: torch.Tensor, src: torch.Tensor, g: torch.Tensor, accumulate: bool = False) -> None:
+    """``out[r] (= | +=) g[r] * src[r]`` over float32 rows, one factor per row."""
+    _need_cuda(out, src, g)
+    _rows_2d(out, "rows")
+    _rows_2d(src, "rows")
+    if out.dtype != torch.float32 or src.dtype != torch.float32 or out.shape != src.shape or g.dtype != torch.float32 \
+            or not g.is_contiguous() or g.numel() < out.shape[0]:
+        raise KernelError("gated_rows: float32 rows of one shape and one float32 factor per row")
+    library("core").call("bfi_gated_rows", _ptr(out), c_long(out.stride(0)), _ptr(src), c_long(src.stride(0)), _ptr(g),
+                         c_int(out.shape[0]), c_int(out.shape[1]), c_int(1 if accumulate else 0), _stream())
+
+
 DECAY_STEP, DECAY_SIGMOID = 1, 2
 
 
@@ -378,13 +390,18 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
                out: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
                n_heads: int, dim: int, vdim: int, heads_per_group: int, mode: int, bias: torch.Tensor,
                rate: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None, q_scale: float = 1.0,
-               inv_tau: float = 1.0, few_tokens: bool = False) -> None:
+               inv_tau: float = 1.0, few_tokens: bool = False, chunk_len: int = 0, max_chunks: int = 0,
+               chunk_state: Optional[torch.Tensor] = None, chunk_decay: Optional[torch.Tensor] = None) -> None:
     """A linear recurrence whose decay depends on the token, over the step's new tokens:
     ``S = diag(a) S + k (c v)^T; o = S^T q + skip * v`` with ``S`` float32
     ``[slots, heads, dim, vdim]`` carried in ``state``.  q and k are columns of ``qk`` (group
     ``h // heads_per_group`` of head ``h``), v of ``v``, the decay's raw value of ``raw`` (rows of one
     storage type).  ``DECAY_STEP``: ``c = softplus(raw_h + bias_h)``, ``a = exp(-rate_h c)``;
-    ``DECAY_SIGMOID``: ``a_d = sigmoid(raw_hd + bias_hd)^inv_tau``, ``c = 1``.  ``out`` float32."""
+    ``DECAY_SIGMOID``: ``a_d = sigmoid(raw_hd + bias_hd)^inv_tau``, ``c = 1``.  ``out`` float32.
+    ``chunk_len`` > 0 runs the chunked form (chunks of a sequence side by side, then a carry over the
+    chunks, then the earlier tokens' part of every output): ``chunk_state`` float32 with
+    ``heads * dim * vdim`` values and ``chunk_decay`` with ``heads * dim`` for every chunk of the step;
+    ``max_chunks`` is the most chunks one sequence has."""
     _need_cuda(qk, v, raw, out, state, cu_seqlens, seq_slot, bias, rate, skip)
     for t, what in ((qk, "q and k"), (v, "values"), (raw, "decay input"), (out, "recurrence output")):
         _rows_2d(t, what)
@@ -405,12 +422,18 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
     _f32_vector(bias, n_raw, "decay_scan: the decay's bias")
     _f32_vector(rate, n_heads, "decay_scan: the decay's rate")
     _f32_vector(skip, n_heads, "decay_scan: the skip factor")
+    if chunk_len > 0:
+        n_chunks = qk.shape[0] // chunk_len + n_seqs
+        for t, per in ((chunk_state, n_heads * dim * vdim), (chunk_decay, n_heads * dim)):
+            if t is None or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() < n_chunks * per or not t.is_cuda:
+                raise KernelError(f"decay_scan: the chunked form needs float32 scratch for {n_chunks} chunks")
     library("core").call("bfi_decay_scan", _ptr(qk), c_long(qk.stride(0)), c_int(q_off), c_int(k_off), _ptr(v),
                          c_long(v.stride(0)), c_int(v_off), _ptr(raw), c_long(raw.stride(0)), c_int(r_off),
                          c_int(dtype_code(qk.dtype)), _ptr(out), c_long(out.stride(0)), _ptr(state), _ptr(cu_seqlens),
                          _ptr(seq_slot), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), c_int(heads_per_group),
                          c_int(mode), c_float(q_scale), c_float(inv_tau), _ptr(bias), _ptr(rate), _ptr(skip),
-                         c_int(1 if few_tokens else 0), _stream())
+                         c_int(1 if few_tokens else 0), c_int(chunk_len), c_int(max_chunks), _ptr(chunk_state),
+                         _ptr(chunk_decay), _stream())
 
 
 def causal_conv(u: torch.Tensor, u_off: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor],
@@ -486,38 +509,62 @@ def moe_route(z: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor
                          c_int(0 if gate is None else 1), _stream())
 
 
-def moe_gate_up(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, token_slot: torch.Tensor,
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor],
+               token_slot: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, top: int, n_groups: int = 1, keep: int = 1,
+               weight_scale: float = 1.0, gate: Optional[torch.Tensor] = None) -> None:
+    """``moe_route`` with the logits made in the same kernel: ``z = w_router h`` with ``w_router``
+    float32 ``[n_experts (+ 1), width]`` (the extra row is the gate's, wanted with ``gate``)."""
+    _need_cuda(h, w_router, correction, token_slot, idx, weight, gate)
+    _rows_2d(h, "router input")
+    n, width = h.shape
+    rows = n_experts + (0 if gate is None else 1)
+    if w_router.dtype != torch.float32 or not w_router.is_contiguous() or w_router.shape != (rows, width):
+        raise KernelError(f"moe_router: the router's rows must be contiguous float32 [{rows}, {width}]")
+    _f32_vector(correction, n_experts, "moe_router: the correction")
+    _i32(token_slot, "token slots")
+    if idx.dtype != torch.int32 or not idx.is_contiguous() or idx.shape != (n, top) or weight.dtype != torch.float32 \
+            or not weight.is_contiguous() or weight.shape != (n, top):
+        raise KernelError("moe_router: idx int32 and weight float32, both contiguous [tokens, top]")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.numel() < n):
+        raise KernelError("moe_router: the gate must be contiguous float32 [tokens]")
+    library("core").call("bfi_moe_router", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_router),
+                         _ptr(correction), _ptr(token_slot), _ptr(idx), _ptr(weight), _ptr(gate), c_int(n), c_int(width),
+                         c_int(n_experts), c_int(top), c_int(n_groups), c_int(keep), c_float(weight_scale),
+                         c_int(0 if gate is None else 1), _stream())
+
+
+def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, n_experts: int, idx: torch.Tensor, token_slot: torch.Tensor,
                 act: torch.Tensor) -> None:
-    """``act[t, k] = silu(w_gate[e] h_t) * (w_up[e] h_t)`` with ``e = idx[t, k]``; the weights are
-    ``[experts, ff, width]``, ``act`` ``[tokens * top, ff]``."""
-    _need_cuda(h, w_gate, w_up, idx, token_slot, act)
+    """``act[t, k] = silu(gate_e h_t) * (up_e h_t)`` with ``e = idx[t, k]``; ``w_gu`` is
+    ``[experts * 2 * ff, width]`` with expert e's gate row j at row ``2 (e ff + j)`` and its up row
+    after it, ``act`` ``[tokens * top, ff]``."""
+    _need_cuda(h, w_gu, idx, token_slot, act)
     _rows_2d(h, "feed-forward input")
     n, width = h.shape
     top = idx.shape[1]
-    ff = w_gate.shape[1]
-    if w_gate.dim() != 3 or w_gate.shape != w_up.shape or w_gate.shape[2] != width or not w_gate.is_contiguous() \
-            or not w_up.is_contiguous() or w_gate.dtype != h.dtype or w_up.dtype != h.dtype:
-        raise KernelError("moe_gate_up: expert weights must be contiguous [experts, ff, width] of the input's dtype")
+    ff = w_gu.shape[0] // (2 * n_experts)
+    if w_gu.dim() != 2 or w_gu.shape != (n_experts * 2 * ff, width) or not w_gu.is_contiguous() or w_gu.dtype != h.dtype:
+        raise KernelError("moe_gate_up: expert weights must be contiguous [experts * 2 * ff, width] of the input's dtype")
     if act.dtype != h.dtype or not act.is_contiguous() or act.shape != (n * top, ff):
         raise KernelError("moe_gate_up: the output must be contiguous [tokens * top, ff] of the input's dtype")
     _i32(idx, "expert choices")
     _i32(token_slot, "token slots")
-    library("core").call("bfi_moe_gate_up", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_gate), _ptr(w_up),
+    library("core").call("bfi_moe_gate_up", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_gu),
                          _ptr(idx), _ptr(token_slot), _ptr(act), c_int(n), c_int(top), c_int(width), c_int(ff), _stream())
 
 
-def moe_down(act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, token_slot: torch.Tensor,
-             out: torch.Tensor, shared_out: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-             accumulate: bool = False) -> None:
-    """``out[t] (= | +=) sum_k weight[t, k] * w_down[idx[t, k]] act[t, k] + gate[t] * shared_out[t]``
-    (the last term only with ``shared_out``; ``gate`` None is 1); ``w_down`` ``[experts, width, ff]``,
-    ``out`` float32 ``[tokens, width]``."""
+def moe_down(act: torch.Tensor, w_down: torch.Tensor, n_experts: int, idx: torch.Tensor, weight: torch.Tensor,
+             token_slot: torch.Tensor, out: torch.Tensor, shared_out: Optional[torch.Tensor] = None,
+             gate: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+    """``out[t] (= | +=) sum_k weight[t, k] * down_e act[t, k] + gate[t] * shared_out[t]`` with
+    ``e = idx[t, k]`` (the last term only with ``shared_out``; ``gate`` None is 1); ``w_down`` is
+    ``[width, experts * ff]`` with expert e's columns at ``e ff``, ``out`` float32 ``[tokens, width]``."""
     _need_cuda(act, w_down, idx, weight, token_slot, out, shared_out, gate)
     _rows_2d(out, "feed-forward output")
     n, top = idx.shape
-    width, ff = w_down.shape[1], w_down.shape[2]
-    if w_down.dim() != 3 or not w_down.is_contiguous() or w_down.dtype != act.dtype:
-        raise KernelError("moe_down: expert weights must be contiguous [experts, width, ff] of the activations' dtype")
+    width, ff = w_down.shape[0], w_down.shape[1] // n_experts
+    if w_down.dim() != 2 or w_down.shape[1] != n_experts * ff or not w_down.is_contiguous() or w_down.dtype != act.dtype:
+        raise KernelError("moe_down: expert weights must be contiguous [width, experts * ff] of the activations' dtype")
     if not act.is_contiguous() or act.shape != (n * top, ff):
         raise KernelError("moe_down: the activations must be contiguous [tokens * top, ff]")
     if out.dtype != torch.float32 or out.shape != (n, width):
@@ -527,7 +574,24 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, weight:
     library("core").call("bfi_moe_down", _ptr(act), c_int(dtype_code(act.dtype)), _ptr(w_down), _ptr(idx), _ptr(weight),
                          _ptr(token_slot), _ptr(shared_out), c_long(0 if shared_out is None else shared_out.stride(0)),
                          _ptr(gate), _ptr(out), c_long(out.stride(0)), c_int(n), c_int(top), c_int(width), c_int(ff),
-                         c_int(1 if accumulate else 0), _stream())
+                         c_int(n_experts), c_int(1 if accumulate else 0), _stream())
+
+
+def moe_weigh_dense(act: torch.Tensor, n_experts: int, idx: torch.Tensor, weight: torch.Tensor,
+                    token_slot: torch.Tensor) -> None:
+    """``act[t, e ff + j] *= (weight of expert e for token t, 0 if it was not chosen)`` over
+    activations ``[tokens, experts * ff]`` that the dense product computed for every expert."""
+    _need_cuda(act, idx, weight, token_slot)
+    _rows_2d(act, "dense expert activations")
+    _i32(idx, "expert choices")
+    _i32(token_slot, "token slots")
+    n, top = idx.shape
+    if act.shape[0] != n or act.shape[1] % n_experts != 0 or weight.dtype != torch.float32 or not weight.is_contiguous() \
+            or weight.shape != (n, top):
+        raise KernelError("moe_weigh_dense: activations [tokens, experts * ff], weights float32 [tokens, top]")
+    library("core").call("bfi_moe_weigh_dense", _ptr(act), c_long(act.stride(0)), c_int(dtype_code(act.dtype)), _ptr(idx),
+                         _ptr(weight), _ptr(token_slot), c_int(n), c_int(top), c_int(n_experts),
+                         c_int(act.shape[1] // n_experts), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:

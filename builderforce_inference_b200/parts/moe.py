@@ -9,11 +9,16 @@ experts' weights are their ``s`` (not renormalised) times ``weight_scale``.  An 
 The shared expert has the same form (its own inner size) and is added multiplied by
 ``sigmoid(W_sg h)``, one number per token.
 
-The router's matrix and the shared expert's gate row are kept as one float32 matrix, so one product
-on the CUDA cores gives the logits and the gate's input in float32.  The experts' products read
-only the chosen experts' weights (``kernels/ops.moe_gate_up``, ``moe_down``); the shared expert runs
-through the dense products.  Nothing here reads a choice back to the host, so a step through this
-part can be captured in a graph.
+The router's matrix and the shared expert's gate row are kept as one float32 matrix; one kernel
+makes the logits and the gate's input from it in float32 and decides (``kernels/ops.moe_router``).  The experts' weights are kept
+as two matrices for all experts (gate and up rows interleaved, expert after expert; the down
+matrices side by side), which serve two ways of computing: a step with few (token, expert) pairs
+reads only the chosen experts' weights (``kernels/ops.moe_gate_up``, ``moe_down``); a bfloat16 step
+with at least ``DENSE_PAIRS_PER_EXPERT`` pairs per expert, which touches nearly every expert anyway,
+runs the two dense products over all experts on the tensor cores and multiplies the activations by
+the chosen experts' weights, 0 for the others, in between (``moe_weigh_dense``).  The shared expert
+runs through the dense products.  Nothing here reads a choice back to the host, so a step through
+this part can be captured in a graph.
 """
 from __future__ import annotations
 
@@ -22,8 +27,11 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
-from ..kernels.linear import EPI_STORE, EPI_SWIGLU, linear
+from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, EPI_SWIGLU, linear
 from .base import FEED_FORWARDS, FeedForward, ParamSpec
+
+
+DENSE_PAIRS_PER_EXPERT = 2      # from this many (token, expert) pairs per expert on, every expert is computed for every token
 
 
 @FEED_FORWARDS.register("routed_mlp")
@@ -60,13 +68,12 @@ class RoutedMLP(FeedForward):
         return specs
 
     def load(self, tensors, runtime) -> None:
-        def stack(kind):
-            mats = [tensors[f"experts.{e}.{kind}"] for e in range(self.n_experts)]
-            if len({m.dtype for m in mats}) > 1 or mats[0].dtype != runtime.dtype:
-                mats = [m.to(runtime.dtype) if runtime.dtype == torch.float32 else m for m in mats]
-            return torch.stack(mats, dim=0).contiguous()
-
-        self.w_gate, self.w_up, self.w_down = stack("gate_proj"), stack("up_proj"), stack("down_proj")
+        mats = [tensors[f"experts.{e}.{kind}"] for e in range(self.n_experts) for kind in ("gate_proj", "up_proj", "down_proj")]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        gu = [torch.stack([mats[3 * e], mats[3 * e + 1]], dim=1).reshape(2 * self.inner, self.width) for e in range(self.n_experts)]
+        self.w_gu = torch.cat(gu, dim=0).contiguous()                                         # [E * 2 * ff, width]
+        self.w_down = torch.cat([mats[3 * e + 2] for e in range(self.n_experts)], dim=1).contiguous()   # [width, E * ff]
         rows = [tensors["router"].float()]
         if self.shared_inner is not None:
             rows.append(tensors["shared.gate"].float())
@@ -87,19 +94,28 @@ class RoutedMLP(FeedForward):
     def _run(self, ctx, h, target, accumulate: bool) -> None:
         n = h.shape[0]
         shared = self.shared_inner is not None
-        z = ctx.rows("moe.logits", self.w_router.shape[0], torch.float32)
-        linear(h, self.w_router, z, EPI_STORE)
         idx = ctx.rows("moe.idx", self.top, torch.int32)
         wts = ctx.rows("moe.weight", self.top, torch.float32)
         gate = ctx.rows("moe.gate", 1, torch.float32).view(-1) if shared else None
-        ops.moe_route(z, self.n_experts, self.correction, idx, wts, self.top, self.n_groups, self.keep_groups,
-                      self.weight_scale, gate)
+        ops.moe_router(h, self.w_router, self.n_experts, self.correction, ctx.token_slot, idx, wts, self.top, self.n_groups,
+                       self.keep_groups, self.weight_scale, gate)
         ys = None
         if shared:
             act_s = ctx.rows("moe.shared.act", self.shared_inner)
             linear(h, self.ws_gate_up, act_s, EPI_SWIGLU)
             ys = ctx.rows("moe.shared.out", self.width, torch.float32)
             linear(act_s, self.ws_down, ys, EPI_STORE)
+        if h.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16 \
+                and n * self.top >= DENSE_PAIRS_PER_EXPERT * self.n_experts:
+            act = ctx.rows("moe.act.dense", self.n_experts * self.inner)
+            linear(h, self.w_gu, act, EPI_SWIGLU)
+            ops.moe_weigh_dense(act, self.n_experts, idx, wts, ctx.token_slot)
+            if shared:      # gate * shared output first, then the experts' sum on top
+                ops.gated_rows(target, ys, gate, accumulate)
+                linear(act, self.w_down, target, EPI_ACCUMULATE)
+            else:
+                linear(act, self.w_down, target, EPI_ACCUMULATE if accumulate else EPI_STORE)
+            return
         act = ctx.rows("moe.act", self.top * self.inner).view(n * self.top, self.inner)
-        ops.moe_gate_up(h, self.w_gate, self.w_up, idx, ctx.token_slot, act)
-        ops.moe_down(act, self.w_down, idx, wts, ctx.token_slot, target, ys, gate, accumulate)
+        ops.moe_gate_up(h, self.w_gu, self.n_experts, idx, ctx.token_slot, act)
+        ops.moe_down(act, self.w_down, self.n_experts, idx, wts, ctx.token_slot, target, ys, gate, accumulate)

@@ -35,8 +35,23 @@ from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, linear
 from .base import MIXERS, Mixer, ParamSpec, StateNeed
 
 
+CHUNK_TOKENS = 64            # chunk length of the chunked recurrence
+CHUNKED_MIN_TOKENS = 192     # a step whose longest piece is shorter walks its tokens in order
+
+
 def _as_f32(t: torch.Tensor) -> torch.Tensor:
     return t.float().contiguous()
+
+
+def _chunking(ctx, per_chunk: int, per_decay: int) -> dict:
+    """The chunked form's arguments for a step with long pieces (none for short steps and single
+    tokens): its scratch comes from the step's workspace."""
+    if ctx.max_seq_tokens < CHUNKED_MIN_TOKENS:
+        return {}
+    n_chunks = ctx.n_tokens // CHUNK_TOKENS + ctx.n_seqs
+    return {"chunk_len": CHUNK_TOKENS, "max_chunks": (ctx.max_seq_tokens + CHUNK_TOKENS - 1) // CHUNK_TOKENS,
+            "chunk_state": ctx.rows("rec.chunk_state", per_chunk, torch.float32, n_rows=n_chunks),
+            "chunk_decay": ctx.rows("rec.chunk_decay", per_decay, torch.float32, n_rows=n_chunks)}
 
 
 @MIXERS.register("state_space")
@@ -106,7 +121,8 @@ class StateSpaceMixer(Mixer):
         y = ctx.rows("ssm.y", inner, torch.float32)
         ops.decay_scan(xbc, inner + gn, inner, xbc, 0, proj, 2 * inner + 2 * gn, y, state, ctx.cu_seqlens, ctx.seq_slot,
                        ctx.n_seqs, self.n_heads, self.state, self.vdim, self.n_heads // self.groups, ops.DECAY_STEP,
-                       self.dt_bias, rate=self.rate, skip=self.skip, few_tokens=ctx.max_seq_tokens == 1)
+                       self.dt_bias, rate=self.rate, skip=self.skip, few_tokens=ctx.max_seq_tokens == 1,
+                       **_chunking(ctx, self.n_heads * self.state * self.vdim, self.n_heads * self.state))
         g = ctx.rows("ssm.gated", inner)
         ops.gated_group_norm(y, proj[:, :inner], self.norm, self.eps, g, self.norm_groups, gate_first=True)
         linear(g, self.w_o, target, epilogue)
@@ -167,7 +183,8 @@ class GatedLinearAttention(Mixer):
         o = ctx.rows("gla.o", vv, torch.float32)
         ops.decay_scan(proj, 0, qk, proj, 2 * qk, z, 0, o, state, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
                        self.n_heads, self.dim, self.vdim, 1, ops.DECAY_SIGMOID, self.a_bias, q_scale=self.dim ** -0.5,
-                       inv_tau=1.0 / self.tau, few_tokens=ctx.max_seq_tokens == 1)
+                       inv_tau=1.0 / self.tau, few_tokens=ctx.max_seq_tokens == 1,
+                       **_chunking(ctx, self.n_heads * self.dim * self.vdim, self.n_heads * self.dim))
         y = ctx.rows("gla.y", vv)
         ops.gated_group_norm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.eps, y, self.n_heads, gate_first=False)
         linear(y, self.w_o, target, epilogue)
