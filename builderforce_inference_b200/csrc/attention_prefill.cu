@@ -19,7 +19,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv,
-                         int window, float scale_log2, float sink_log2) {
+                         int window, int chunk, float scale_log2, float sink_log2, const float* __restrict__ sinks) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -42,7 +42,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
 
     const int seq_hi = start + nt - 1;                                   // last key the cache holds for this sequence
     const int hi_block = start + min(tok0 + AP_QROWS - 1, nt - 1);       // last key any row of the block reads
-    const int lo_block = window > 0 ? max(0, start + tok0 - window + 1) : 0;
+    int lo_block = window > 0 ? max(0, start + tok0 - window + 1) : 0;
+    if (chunk > 0) lo_block = max(lo_block, (start + tok0) / chunk * chunk);     // a token reads its own chunk of positions only
     const int p_beg = lo_block / AD_TILE, p_end = hi_block / AD_TILE;    // inclusive
 
     // ---- Q tile -> shared memory (rows past the sequence are zero)
@@ -76,9 +77,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
     for (int r = 0; r < 2; ++r) {
         pos_r[r] = start + tok0 + warp * 16 + g + r * 8;
         lo_r[r] = window > 0 ? max(0, pos_r[r] - window + 1) : 0;
+        if (chunk > 0) lo_r[r] = max(lo_r[r], pos_r[r] / chunk * chunk);
     }
     const int warp_pos_max = start + tok0 + warp * 16 + 15;
-    const int warp_lo_min = window > 0 ? max(0, start + tok0 + warp * 16 - window + 1) : 0;
+    int warp_lo_min = window > 0 ? max(0, start + tok0 + warp * 16 - window + 1) : 0;
+    if (chunk > 0) warp_lo_min = max(warp_lo_min, (start + tok0 + warp * 16) / chunk * chunk);
+    // the largest lower limit any row of the warp has: keys below it need the mask
+    int warp_lo_max = window > 0 ? warp_pos_max - window + 1 : 0;
+    if (chunk > 0) warp_lo_max = max(warp_lo_max, warp_pos_max / chunk * chunk);
 
     uint32_t qa[D / 16][4];
     float m_run[2] = {-INFINITY, -INFINITY};
@@ -139,7 +145,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                 }
             }
             // ---- mask (only where the page crosses a row's limits) and online softmax
-            const bool need_mask = key_hi > start + tok0 + warp * 16 || key_lo < (window > 0 ? warp_pos_max - window + 1 : 0);
+            const bool need_mask = key_hi > start + tok0 + warp * 16 || key_lo < warp_lo_max;
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 float mx = -INFINITY;
@@ -206,7 +212,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
         const int tok = tok0 + warp * 16 + g + r * 8;
         if (tok >= nt) continue;
         // the sink's term of the denominator (no sink: -inf, which adds 0)
-        const float l_all = l_run[r] + (m_run[r] == -INFINITY ? 0.0f : fast_exp2(sink_log2 - m_run[r]));
+        const float sk = sinks != nullptr ? sinks[head] * 1.4426950408889634f : sink_log2;      // one sink per head, or one for all
+        const float l_all = l_run[r] + (m_run[r] == -INFINITY ? 0.0f : fast_exp2(sk - m_run[r]));
         const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
         bf16* orow = out + (size_t)(t0 + tok) * out_stride + (size_t)head * D;
 #pragma unroll
@@ -221,7 +228,7 @@ template <int D>
 static int launch_prefill(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                           const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                           const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv,
-                          int window, float scale, float sink, cudaStream_t stream) {
+                          int window, int chunk, float scale, float sink, const float* sinks, cudaStream_t stream) {
     const size_t smem = (size_t)(AP_QROWS * D + 4 * AD_TILE * D) * sizeof(bf16);
     auto kernel = attention_prefill_kernel<D>;
     if (smem > 48 * 1024) {
@@ -232,20 +239,22 @@ static int launch_prefill(const void* q, long q_stride, void* out, long out_stri
     dim3 grid((max_tokens + AP_QROWS - 1) / AP_QROWS, n_q, n_seqs);
     bfi_launch(kernel, grid, dim3(AD_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, cu_seqlens, seq_slot, seq_start, n_q,
-               n_kv, window, scale * 1.4426950408889634f, sink * 1.4426950408889634f);
+               n_kv, window, chunk, scale * 1.4426950408889634f, sink * 1.4426950408889634f, sinks);
     return bfi_check_launch("attention_prefill");
 }
 
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
-// `sink`: a score beside the keys' whose exponential joins the softmax's denominator; -infinity for none.
+// `sink`: a score beside the keys' whose exponential joins the softmax's denominator; -infinity for none;
+// `sinks` (float32, one per query head) takes its place when given.  `chunk` > 0: a token reads only
+// the keys of its own block of `chunk` consecutive positions, blocks counted from position 0.
 extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                           const void* v_pages, const int* block_table, int table_stride,
                                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
-                                          int max_tokens, int n_q, int n_kv, int d, int window, float scale, float sink,
-                                          cudaStream_t stream) {
+                                          int max_tokens, int n_q, int n_kv, int d, int window, int chunk, float scale,
+                                          float sink, const float* sinks, cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
-    BFI_REQUIRE(window >= 0, "attention_prefill: negative window");
+    BFI_REQUIRE(window >= 0 && chunk >= 0, "attention_prefill: negative window or chunk");
     if (n_seqs <= 0 || max_tokens <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || n_seqs > 65535 ||
@@ -253,7 +262,7 @@ extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* ou
         return 2;
     if (d == 64)
         return launch_prefill<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, sink, stream);
+                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, stream);
     return launch_prefill<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, scale, sink, stream);
+                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, stream);
 }

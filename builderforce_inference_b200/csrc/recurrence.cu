@@ -155,10 +155,26 @@ __global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict_
 // The same three phases with the state in registers, for D up to 128: a warp owns 32 columns of one
 // head of one sequence (or chunk), lane l holds all D rows of column v0 + l, so a token's output
 // value is one thread's sum and the warp never waits for another.  The lanes share the work of
-// fetching the token's q, k and decay input (lane l fetches rows l, l + 32, ..., one token ahead of
-// the arithmetic) and of evaluating the decay, and pass them to each other through the warp's own
+// fetching the token's q, k and decay input (lane l fetches rows l R .. l R + R - 1, one token ahead
+// of the arithmetic) and of evaluating the decay, and pass them to each other through the warp's own
 // piece of shared memory.
 #define REC_WARPS 4
+
+// R neighbouring values of storage type T by one load; p is aligned to R * sizeof(T) bytes
+template <typename T, int R>
+__device__ __forceinline__ void rec_load_rows(const T* __restrict__ p, T (&dst)[R]) {
+    constexpr int BYTES = sizeof(T) * R;
+    if constexpr (BYTES == 16) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
+    } else if constexpr (BYTES == 8) {
+        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p);
+    } else if constexpr (BYTES == 4) {
+        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(p);
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) dst[i] = p[i];
+    }
+}
 
 template <typename T, int PHASE, int MODE, int DMAX>
 __global__ void __launch_bounds__(REC_WARPS * 32)
@@ -205,76 +221,104 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
 #pragma unroll
         for (int d = 0; d < DMAX; ++d) S[d] = (PHASE == 3 && col_ok && d < D) ? sp[(size_t)d * V] : 0.0f;
     }
-    // the decay's constants of this lane's rows, and the running product of the chunk's decays
+    // the decay's constants of this lane's rows (rows lane * R .. lane * R + R - 1), and the running
+    // product of the chunk's decays
     float bias_r[R], prod[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int d = lane + 32 * i;
+        const int d = lane * R + i;
         bias_r[i] = (MODE == REC_DECAY_SIGMOID && d < D) ? a.bias[(size_t)h * D + d] : 0.0f;
         prod[i] = 1.0f;
     }
     const float bias_h = MODE == REC_DECAY_STEP ? a.bias[h] : 0.0f;
     const float rate_h = MODE == REC_DECAY_STEP ? a.rate[h] : 0.0f;
-    // the first token's inputs
-    float nq[R], nk[R], nr[R], nv = 0.0f, nstep = 0.0f;
+    // a lane's R rows are R neighbours in memory: one load each for q, k and the decay input where
+    // every token's rows are aligned to it (and D is whole lanes' worth), single values otherwise
+    const size_t vec_bytes = sizeof(T) * R;
+    const bool vec = R > 1 && D % R == 0 && a.qk_stride % R == 0 && a.r_stride % R == 0 && a.q_off % R == 0 && a.k_off % R == 0 &&
+                     a.r_off % R == 0 && ((uintptr_t)qk % vec_bytes) == 0 && ((uintptr_t)raw % vec_bytes) == 0;
+    // the next token's inputs stay as they were fetched (storage type) until they are used, so the
+    // loads are in flight while this token's arithmetic runs
+    __align__(16) T nq[R];
+    __align__(16) T nk[R];
+    __align__(16) T nr[R];
+    T nv = from_f32<T>(0.0f), nstep = from_f32<T>(0.0f);
+    float nold = 0.0f;
     auto fetch = [&](int t) {
         const size_t tok = (size_t)(t0 + t);
         const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
         const T* rr = raw + tok * a.r_stride + a.r_off;
+        const int d0 = lane * R;
+        if (vec) {
+            if (d0 < D) {
+                rec_load_rows<T, R>(row + a.q_off + d0, nq);
+                if (PHASE != 3) rec_load_rows<T, R>(row + a.k_off + d0, nk);
+                if (MODE == REC_DECAY_SIGMOID) rec_load_rows<T, R>(rr + (size_t)h * D + d0, nr);
+            }
+        } else {
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int d = lane + 32 * i;
-            nq[i] = d < D ? to_f32(row[a.q_off + d]) : 0.0f;
-            nk[i] = (PHASE != 3 && d < D) ? to_f32(row[a.k_off + d]) : 0.0f;
-            nr[i] = (MODE == REC_DECAY_SIGMOID && d < D) ? to_f32(rr[(size_t)h * D + d]) : 0.0f;
+            for (int i = 0; i < R; ++i) {
+                const int d = d0 + i;
+                if (d < D) {
+                    nq[i] = row[a.q_off + d];
+                    if (PHASE != 3) nk[i] = row[a.k_off + d];
+                    if (MODE == REC_DECAY_SIGMOID) nr[i] = rr[(size_t)h * D + d];
+                }
+            }
         }
-        if (MODE == REC_DECAY_STEP) nstep = to_f32(rr[h]);
-        nv = (PHASE != 3 && col_ok) ? to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + col]) : 0.0f;
+        if (MODE == REC_DECAY_STEP) nstep = rr[h];
+        if (PHASE != 3 && col_ok) nv = vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + col];
+        if (PHASE == 3 && col_ok) nold = out[tok * a.out_stride + (size_t)h * V + col];
     };
+#pragma unroll
+    for (int i = 0; i < R; ++i) nq[i] = nk[i] = nr[i] = from_f32<T>(0.0f);
     if (nt > 0) fetch(0);
     for (int t = 0; t < nt; ++t) {
         float step_c = 1.0f, w_h = 1.0f;
         if (MODE == REC_DECAY_STEP) {
-            step_c = rec_softplus(nstep + bias_h);
+            step_c = rec_softplus(to_f32(nstep) + bias_h);
             w_h = expf(-rate_h * step_c);
         }
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const int d = lane + 32 * i;
-            float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(nr[i] + bias_r[i]) * a.inv_tau);
+            const int d = lane * R + i;
+            float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(to_f32(nr[i]) + bias_r[i]) * a.inv_tau);
             if (d >= D) w = 1.0f;
             if (PHASE != 0) prod[i] *= w;
-            qs[d] = nq[i] * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f);
-            ks[d] = nk[i];
+            qs[d] = d < D ? to_f32(nq[i]) * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f) : 0.0f;
+            ks[d] = d < D ? to_f32(nk[i]) : 0.0f;
             as[d] = w;
         }
-        const float vv = nv;
+        const float old = nold;
+        const float vv = to_f32(nv);
         __syncwarp();
         if (t + 1 < nt) fetch(t + 1);
         const float cv = step_c * vv;
-        float acc = 0.0f;
+        // four partial sums, so that a token's sum is four chains of D / 4 dependent operations
+        float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
 #pragma unroll
         for (int d4 = 0; d4 < DMAX; d4 += 4) {
             if (d4 < D) {
                 const float4 q4 = *reinterpret_cast<const float4*>(qs + d4);
                 if (PHASE == 3) {
-                    acc = fmaf(S[d4], q4.x, acc), acc = fmaf(S[d4 + 1], q4.y, acc);
-                    acc = fmaf(S[d4 + 2], q4.z, acc), acc = fmaf(S[d4 + 3], q4.w, acc);
+                    acc0 = fmaf(S[d4], q4.x, acc0), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
+                    acc2 = fmaf(S[d4 + 2], q4.z, acc2), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
                 } else {
                     const float4 k4 = *reinterpret_cast<const float4*>(ks + d4);
                     float4 a4;
                     if (MODE == REC_DECAY_STEP) a4 = make_float4(w_h, w_h, w_h, w_h);
                     else a4 = *reinterpret_cast<const float4*>(as + d4);
-                    S[d4] = fmaf(a4.x, S[d4], k4.x * cv), acc = fmaf(S[d4], q4.x, acc);
-                    S[d4 + 1] = fmaf(a4.y, S[d4 + 1], k4.y * cv), acc = fmaf(S[d4 + 1], q4.y, acc);
-                    S[d4 + 2] = fmaf(a4.z, S[d4 + 2], k4.z * cv), acc = fmaf(S[d4 + 2], q4.z, acc);
-                    S[d4 + 3] = fmaf(a4.w, S[d4 + 3], k4.w * cv), acc = fmaf(S[d4 + 3], q4.w, acc);
+                    S[d4] = fmaf(a4.x, S[d4], k4.x * cv), acc0 = fmaf(S[d4], q4.x, acc0);
+                    S[d4 + 1] = fmaf(a4.y, S[d4 + 1], k4.y * cv), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
+                    S[d4 + 2] = fmaf(a4.z, S[d4 + 2], k4.z * cv), acc2 = fmaf(S[d4 + 2], q4.z, acc2);
+                    S[d4 + 3] = fmaf(a4.w, S[d4 + 3], k4.w * cv), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
                 }
             }
         }
+        const float acc = (acc0 + acc1) + (acc2 + acc3);
         if (col_ok) {
             float* dst = out + (size_t)(t0 + t) * a.out_stride + (size_t)h * V + col;
-            if (PHASE == 3) *dst += acc;
+            if (PHASE == 3) *dst = old + acc;
             else *dst = fmaf(skip, vv, acc);
         }
         __syncwarp();
@@ -287,7 +331,7 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
     if (PHASE == 1 && unit == h * a.v_blocks) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const int d = lane + 32 * i;
+            const int d = lane * R + i;
             if (d < D) chunk_decay[(chunk_no * a.H + h) * D + d] = prod[i];
         }
     }

@@ -231,13 +231,15 @@ def attention_decode_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n
 def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sink=None) -> bool:
     """Tensor-core attention for steps that bring more than one token per sequence."""
     d = kv.head_dim
-    if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
+    if d not in (64, 128) or kv.value_dim != d or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False
+    sinks = sink if isinstance(sink, torch.Tensor) else None        # float32, one per query head
     return library("fast").call_optional(
         "bfi_attention_prefill_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot),
         _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads),
-        c_int(d), c_int(kv.window or 0), c_float(scale), _sink(sink), _stream())
+        c_int(d), c_int(kv.window or 0), c_int(kv.chunk or 0), c_float(scale), _sink(None if sinks is not None else sink),
+        _ptr(sinks), _stream())
 
 
 TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles

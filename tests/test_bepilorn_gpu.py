@@ -136,6 +136,34 @@ def test_chunked_sink_attention_kernel_in_a_mixed_batch(dt, n_q, n_kv, d, dv, ch
     assert rel_err(got, torch.cat(refs)) < (3e-6 if dt == F32 else 1e-2)
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,chunk", [(8, 2, 64, 128), (4, 4, 128, 70), (2, 1, 64, 9), (4, 2, 128, None)])
+def test_tensor_core_prompt_attention_with_chunks_and_a_sink_per_head(n_q, n_kv, d, chunk):
+    """The bfloat16 kernel that steps with more than one token per sequence run when keys and values
+    have one size of 64 or 128: the same mixed batch as above, through the choice the attention part makes."""
+    from builderforce_inference_b200.engine.context import Workspace, build_context
+    from builderforce_inference_b200.kernels import attention as choose
+    from builderforce_inference_b200.kernels.library import library
+    g = torch.Generator().manual_seed(n_q + d)
+    seqs = [(2, 0, 150), (0, 130, 2), (1, 61, 7)]
+    pages = Pages(3, 256, n_kv, d, d, BF16, chunk)
+    sink = torch.randn(n_q, generator=g)
+    qs, refs = [], []
+    for slot, start, t in seqs:
+        k, v, q = (torch.randn(start + t, h, d, generator=g) for h in (n_kv, n_kv, n_q))
+        pages.write(slot, 0, k, v)
+        kk, vv = pages.read(slot, start + t)
+        ref = P.chunk_sink_attention(q64(q, BF16), kk, vv, 0.2, chunk, sink.double())
+        refs.append(ref[start:].reshape(t, n_q * d))
+        qs.append(q[start:].reshape(t, n_q * d))
+    ctx = build_context([(slot, start, [0] * t) for slot, start, t in seqs], BF16, Workspace(DEV), DEV)
+    qd = torch.cat(qs).to(BF16).to(DEV)
+    out = torch.full((qd.shape[0], n_q * d), float("nan"), dtype=BF16, device=DEV)
+    before = library("fast").calls
+    assert choose.attend(ctx, qd, out, pages.view, n_q, 0.2, sink.float().to(DEV))
+    assert library("fast").calls == before + 1
+    assert rel_err(out, torch.cat(refs)) < 1.5e-2
+
+
 @pytest.mark.parametrize("dt", [F32, BF16])
 @pytest.mark.parametrize("chunk", [5, 64, 65, 100])
 def test_one_loud_key_just_inside_and_just_outside_the_chunk(dt, chunk):
