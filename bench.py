@@ -348,7 +348,8 @@ def bepilorn_config(width, heads, kv, d, ff, layers):
     pair = {"left": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": DESIGN_WINDOW},
                      "rot": {"base": 1e6, "dims": d // 2}},
             "right": {"heads": heads, "dim": d, "vdim": d, "tau": 16.0, "rank": 64}, "left_scale": 0.6, "right_scale": 1.1}
-    mlp = {"kind": "moe", "expert": {"ff": ff // 6}, "shared": {"ff": ff - 4 * (ff // 6)},
+    expert_ff = ff // 6 // 128 * 128            # a sixth of the dense inner size, in whole tiles
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": ff - 4 * expert_ff},
            "router": {"experts": BEPILORN_EXPERTS, "top": 4, "groups": {"count": 4, "keep": 2}}}
     return {"architecture": "Bepilorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.25,
             "layers": [{"type": "parallel" if i % 4 == 3 else "mamba2", "mixer": pair if i % 4 == 3 else ssm, "mlp": mlp}

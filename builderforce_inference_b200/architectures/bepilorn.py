@@ -26,7 +26,7 @@ NORM_OFFSET = 1.0       # the block norms' weights are stored around zero
 
 def bepilorn_spec(cfg: BepilornConfig) -> ModelSpec:
     norm = PartSpec("rms", {"width": cfg.width, "eps": cfg.eps, "offset": NORM_OFFSET})
-    layers = []
+    layers, unused = [], []
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         names = {"norm1.weight": p + "norm1", "norm1b.weight": p + "norm1b"}
@@ -63,7 +63,7 @@ def bepilorn_spec(cfg: BepilornConfig) -> ModelSpec:
         params = {"norm1": norm, "mixer": mixer, "norm1b": norm}
         if layer.mlp is not None:
             f = layer.mlp
-            params.update({"norm2": norm, "norm2b": norm, "ffn": PartSpec("routed_mlp", {
+            params.update({"norm2": norm, "norm2b": norm, "ffn": PartSpec("mixture_of_experts", {
                 "width": cfg.width, "n_experts": f.experts, "top": f.top, "inner": f.ff, "n_groups": f.groups,
                 "keep_groups": f.keep, "shared_inner": f.shared_ff})})
             q = p + "mlp."
@@ -75,11 +75,13 @@ def bepilorn_spec(cfg: BepilornConfig) -> ModelSpec:
             if f.shared_ff is not None:
                 names.update({"ffn.shared.gate_proj": q + "shared.gate", "ffn.shared.up_proj": q + "shared.up",
                               "ffn.shared.down_proj": q + "shared.down", "ffn.shared.gate": q + "shared.sg"})
+        else:       # a checkpoint may still carry the norms of the feed-forward the layer does not have
+            unused += [p + "norm2", p + "norm2b"]
         layers.append(LayerSpec(block=PartSpec("sandwich", params), names=names))
     return ModelSpec(
         vocab_size=cfg.vocab, width=cfg.width, embedding_name="embed", layers=tuple(layers),
         schedule=tuple(RunSpec(layer=i) for i in range(len(layers))),
-        final_norm=norm, final_norm_names={"weight": "final.norm"}, head_name="head",
+        final_norm=norm, final_norm_names={"weight": "final.norm"}, head_name="head", ignored_names=tuple(unused),
         max_positions=cfg.max_positions, stop_ids=tuple(cfg.eos_token_ids), logit_scale=cfg.logit_scale)
 
 

@@ -98,7 +98,7 @@ def _state_space(r: ConfigReader) -> BepilornStateSpace:
     parts = r.integer("norm_groups", default=1, minimum=1)
     if (heads * vdim) % parts != 0:
         raise ConfigError(f"{r.what}: heads * vdim = {heads * vdim} does not cut into {parts} norm_groups")
-    conv = r.integer("conv", minimum=2)
+    conv = r.integer("conv", minimum=1)
     if conv > 16:
         raise ConfigError(f"{r.what}: key 'conv' must be at most 16 taps, got {conv}")
     return BepilornStateSpace(heads=heads, vdim=vdim, state=r.integer("state", minimum=1), groups=groups, conv=conv,

@@ -138,49 +138,56 @@ extern "C" int bfi_moe_route(const float* z, long z_stride, const float* correct
 template <typename T>
 __device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* __restrict__ x, int n, int lane);
 
+// (x is 16-byte aligned; the loops are unrolled so that several of a row's loads are in flight at once)
 template <>
 __device__ __forceinline__ float warp_dot<float>(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
-    float acc = 0.0f;
+    float acc0 = 0.0f, acc1 = 0.0f;
     if ((n & 3) == 0 && ((uintptr_t)w & 15) == 0) {
+#pragma unroll 4
         for (int j = lane * 4; j < n; j += 128) {
-            const float4 a = *reinterpret_cast<const float4*>(w + j);
-            acc = fmaf(a.x, x[j], acc), acc = fmaf(a.y, x[j + 1], acc), acc = fmaf(a.z, x[j + 2], acc), acc = fmaf(a.w, x[j + 3], acc);
+            const float4 a = __ldg(reinterpret_cast<const float4*>(w + j));
+            const float4 b = *reinterpret_cast<const float4*>(x + j);
+            acc0 = fmaf(a.x, b.x, acc0), acc1 = fmaf(a.y, b.y, acc1), acc0 = fmaf(a.z, b.z, acc0), acc1 = fmaf(a.w, b.w, acc1);
         }
     } else {
-        for (int j = lane; j < n; j += 32) acc = fmaf(w[j], x[j], acc);
+#pragma unroll 4
+        for (int j = lane; j < n; j += 32) acc0 = fmaf(w[j], x[j], acc0);
     }
-    return warp_sum(acc);
+    return warp_sum(acc0 + acc1);
 }
 template <>
 __device__ __forceinline__ float warp_dot<bf16>(const bf16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
-    float acc = 0.0f;
+    float acc0 = 0.0f, acc1 = 0.0f;
     if ((n & 7) == 0 && ((uintptr_t)w & 15) == 0) {
+#pragma unroll 4
         for (int j = lane * 8; j < n; j += 256) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(w + j);
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(w + j));
             const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(p[i]);
-                acc = fmaf(f.x, x[j + 2 * i], acc), acc = fmaf(f.y, x[j + 2 * i + 1], acc);
-            }
+            const float4 b0 = *reinterpret_cast<const float4*>(x + j);
+            const float4 b1 = *reinterpret_cast<const float4*>(x + j + 4);
+            const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]);
+            const float2 f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
+            acc0 = fmaf(f0.x, b0.x, acc0), acc1 = fmaf(f0.y, b0.y, acc1), acc0 = fmaf(f1.x, b0.z, acc0), acc1 = fmaf(f1.y, b0.w, acc1);
+            acc0 = fmaf(f2.x, b1.x, acc0), acc1 = fmaf(f2.y, b1.y, acc1), acc0 = fmaf(f3.x, b1.z, acc0), acc1 = fmaf(f3.y, b1.w, acc1);
         }
     } else {
-        for (int j = lane; j < n; j += 32) acc = fmaf(__bfloat162float(w[j]), x[j], acc);
+#pragma unroll 4
+        for (int j = lane; j < n; j += 32) acc0 = fmaf(__bfloat162float(w[j]), x[j], acc0);
     }
-    return warp_sum(acc);
+    return warp_sum(acc0 + acc1);
 }
 
 // The router's logits and its decision in one kernel: one block per token, the token's input as
 // float32 in shared memory, a warp per logit (router rows are float32 [E (+1), width]), then warp 0
 // decides.  The logits are float32 sums of float32 products of the input as its storage type holds it.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_router_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ w_router,
                   const float* __restrict__ correction, const int* __restrict__ token_slot, int* __restrict__ idx,
                   float* __restrict__ weight, float* __restrict__ gate, int width, int E, int top, int n_groups, int keep,
                   float weight_scale, int extra) {
     pdl_trigger();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float* hs = sm;                                // [width]
     float* z = hs + width;                         // [E + 1]
     float* scratch = z + E + 1;                    // [2 E + n_groups]
@@ -216,12 +223,12 @@ extern "C" int bfi_moe_router(const void* h, long h_stride, int dtype, const flo
     if (dtype == BFI_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
-            bfi_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)h, h_stride, w_router, correction,
+            bfi_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, (const float*)h, h_stride, w_router, correction,
                        token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
-            bfi_launch(moe_router_kernel<bf16>, dim3(n_tokens), dim3(128), smem, stream, (const bf16*)h, h_stride, w_router, correction,
+            bfi_launch(moe_router_kernel<bf16>, dim3(n_tokens), dim3(256), smem, stream, (const bf16*)h, h_stride, w_router, correction,
                        token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
     }
     if (e != cudaSuccess) return bfi_fail("moe_router: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -237,7 +244,7 @@ moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__
                    const int* __restrict__ idx, const int* __restrict__ token_slot, T* __restrict__ act, int top,
                    int width, int ff, int rows_per_block) {
     pdl_trigger();
-    extern __shared__ float hs[];                  // [width]
+    extern __shared__ __align__(16) float hs[];    // [width]
     const int pair = blockIdx.x;
     const int t = pair / top;
     if (token_slot[t] < 0) return;                 // padding row
@@ -297,7 +304,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
                 long shared_stride, const float* __restrict__ gate, float* __restrict__ out, long out_stride, int top,
                 int width, int ff, int n_experts, int cols_per_block, int accumulate) {
     pdl_trigger();
-    extern __shared__ float as[];                  // [top][ff]
+    extern __shared__ __align__(16) float as[];    // [top][ff]
     const int t = blockIdx.x;
     if (token_slot[t] < 0) return;
     pdl_wait();

@@ -337,6 +337,88 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
     }
 }
 
+// One new token per sequence: the state never rests anywhere.  A warp owns 32 columns of one head of
+// one sequence and streams the rows of its columns through once: read, decay, add, multiply by q, write.
+// The rows are asked for eight at a time so that a step's traffic, which is the states read and
+// written once, streams.
+#define REC_STEP_DMAX 512
+template <typename T, int MODE>
+__global__ void __launch_bounds__(REC_WARPS * 32)
+decay_step_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, const T* __restrict__ raw, float* __restrict__ out,
+                  float* __restrict__ state, const RecArgs a) {
+    pdl_trigger();
+    extern __shared__ __align__(16) float step_stage[];          // [REC_WARPS][3][D rounded up to 4]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int unit = blockIdx.x * REC_WARPS + warp;
+    const int seq = blockIdx.y;
+    const int slot = a.seq_slot[seq];
+    if (slot < 0 || unit >= a.H * a.v_blocks) return;
+    const int D = a.D, V = a.V, Dp = (D + 3) & ~3;
+    const int h = unit / a.v_blocks;
+    const int col = (unit - h * a.v_blocks) * 32 + lane;
+    const bool col_ok = col < V;
+    const int grp = h / a.heads_per_group;
+    float* qs = step_stage + (size_t)warp * 3 * Dp;
+    float* ks = qs + Dp;
+    float* as = ks + Dp;
+    float* sp = state + (((size_t)slot * a.H + h) * D) * V + col;
+    pdl_wait();
+    const size_t tok = (size_t)a.cu_seqlens[seq];
+    const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
+    const T* rr = raw + tok * a.r_stride + a.r_off;
+    float step_c = 1.0f, w_h = 1.0f;
+    if (MODE == REC_DECAY_STEP) {
+        step_c = rec_softplus(to_f32(rr[h]) + a.bias[h]);
+        w_h = expf(-a.rate[h] * step_c);
+    }
+    for (int d = lane; d < Dp; d += 32) {
+        const bool in = d < D;
+        qs[d] = in ? to_f32(row[a.q_off + d]) * a.q_scale : 0.0f;
+        ks[d] = in ? to_f32(row[a.k_off + d]) : 0.0f;
+        as[d] = !in ? 1.0f : (MODE == REC_DECAY_STEP ? w_h
+                               : expf(rec_log_sigmoid(to_f32(rr[(size_t)h * D + d]) + a.bias[(size_t)h * D + d]) * a.inv_tau));
+    }
+    const float vv = col_ok ? to_f32(vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + col]) : 0.0f;
+    __syncwarp();
+    if (!col_ok) return;
+    const float cv = step_c * vv;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    int d = 0;
+    for (; d + 8 <= D; d += 8) {
+        float sv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sv[i] = sp[(size_t)(d + i) * V];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sv[i] = fmaf(as[d + i], sv[i], ks[d + i] * cv);
+            sp[(size_t)(d + i) * V] = sv[i];
+            if (i & 1) acc1 = fmaf(sv[i], qs[d + i], acc1);
+            else acc0 = fmaf(sv[i], qs[d + i], acc0);
+        }
+    }
+    for (; d < D; ++d) {
+        const float s1 = fmaf(as[d], sp[(size_t)d * V], ks[d] * cv);
+        sp[(size_t)d * V] = s1;
+        acc0 = fmaf(s1, qs[d], acc0);
+    }
+    out[tok * a.out_stride + (size_t)h * V + col] = fmaf(a.skip ? a.skip[h] : 0.0f, vv, acc0 + acc1);
+}
+
+template <typename T>
+static int launch_decay_step(const void* qk, const void* vsrc, const void* raw, float* out, float* state, RecArgs a, int n_seqs,
+                             cudaStream_t stream) {
+    a.vb = 32, a.v_blocks = (a.V + 31) / 32;
+    const dim3 grid((a.H * a.v_blocks + REC_WARPS - 1) / REC_WARPS, n_seqs), block(REC_WARPS * 32);
+    const size_t smem = (size_t)REC_WARPS * 3 * ((a.D + 3) & ~3) * sizeof(float);
+    if (a.mode == REC_DECAY_STEP)
+        bfi_launch(decay_step_kernel<T, REC_DECAY_STEP>, grid, block, smem, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out,
+                   state, a);
+    else
+        bfi_launch(decay_step_kernel<T, REC_DECAY_SIGMOID>, grid, block, smem, stream, (const T*)qk, (const T*)vsrc, (const T*)raw,
+                   out, state, a);
+    return bfi_check_launch("decay_scan (single tokens)");
+}
+
 // One thread per element of a head's state: S = state[slot]; for every chunk of the sequence in
 // order: the chunk's place receives S (the state it starts from) and S = decay_row * S + what the
 // chunk adds; at the end state[slot] = S.
@@ -465,6 +547,11 @@ extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_o
     a.H = H, a.D = D, a.V = V, a.heads_per_group = heads_per_group, a.mode = mode;
     a.q_scale = q_scale, a.inv_tau = inv_tau, a.bias = bias, a.rate = rate, a.skip = skip;
     a.cu_seqlens = cu_seqlens, a.seq_slot = seq_slot, a.chunk_len = chunk_len;
+    if (few_tokens == 2 && D <= REC_STEP_DMAX && !g_rec_general && n_seqs <= 65535) {
+        // every sequence brings exactly one token
+        if (dtype == BFI_F32) return launch_decay_step<float>(qk, vsrc, raw, out, state, a, n_seqs, stream);
+        return launch_decay_step<bf16>(qk, vsrc, raw, out, state, a, n_seqs, stream);
+    }
     if (D <= 128 && !g_rec_general && (long)H * ((V + 31) / 32) <= 2147483647L && n_seqs <= 65535) {
         // the state in registers, a warp per 32 columns
         const int chunks_r = chunk_len > 0 ? max_chunks : 0;
@@ -474,7 +561,7 @@ extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_o
     }
     // columns per block: few where the step is short (more blocks share the state's traffic)
     int vb = V;
-    const int want = few_tokens ? 16 : 32;
+    const int want = few_tokens ? 16 : 32;      // few_tokens: 1 = no sequence brings more than one token, 2 = each brings exactly one
     if (V > want) vb = want;
     const int v_blocks = (V + vb - 1) / vb;
     int threads = vb * (256 / vb > 0 ? 256 / vb : 1);

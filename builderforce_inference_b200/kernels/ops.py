@@ -390,7 +390,8 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
                out: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int,
                n_heads: int, dim: int, vdim: int, heads_per_group: int, mode: int, bias: torch.Tensor,
                rate: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None, q_scale: float = 1.0,
-               inv_tau: float = 1.0, few_tokens: bool = False, chunk_len: int = 0, max_chunks: int = 0,
+               inv_tau: float = 1.0, few_tokens: bool = False, single_tokens: bool = False, chunk_len: int = 0,
+               max_chunks: int = 0,
                chunk_state: Optional[torch.Tensor] = None, chunk_decay: Optional[torch.Tensor] = None) -> None:
     """A linear recurrence whose decay depends on the token, over the step's new tokens:
     ``S = diag(a) S + k (c v)^T; o = S^T q + skip * v`` with ``S`` float32
@@ -401,7 +402,8 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
     ``chunk_len`` > 0 runs the chunked form (chunks of a sequence side by side, then a carry over the
     chunks, then the earlier tokens' part of every output): ``chunk_state`` float32 with
     ``heads * dim * vdim`` values and ``chunk_decay`` with ``heads * dim`` for every chunk of the step;
-    ``max_chunks`` is the most chunks one sequence has."""
+    ``max_chunks`` is the most chunks one sequence has.  ``single_tokens``: every sequence of the
+    step brings exactly one token (the state is then streamed through once)."""
     _need_cuda(qk, v, raw, out, state, cu_seqlens, seq_slot, bias, rate, skip)
     for t, what in ((qk, "q and k"), (v, "values"), (raw, "decay input"), (out, "recurrence output")):
         _rows_2d(t, what)
@@ -432,7 +434,8 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
                          c_int(dtype_code(qk.dtype)), _ptr(out), c_long(out.stride(0)), _ptr(state), _ptr(cu_seqlens),
                          _ptr(seq_slot), c_int(n_seqs), c_int(n_heads), c_int(dim), c_int(vdim), c_int(heads_per_group),
                          c_int(mode), c_float(q_scale), c_float(inv_tau), _ptr(bias), _ptr(rate), _ptr(skip),
-                         c_int(1 if few_tokens else 0), c_int(chunk_len), c_int(max_chunks), _ptr(chunk_state),
+                         c_int(2 if single_tokens else (1 if few_tokens else 0)), c_int(chunk_len), c_int(max_chunks),
+                         _ptr(chunk_state),
                          _ptr(chunk_decay), _stream())
 
 

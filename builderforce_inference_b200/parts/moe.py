@@ -34,7 +34,7 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec
 DENSE_PAIRS_PER_EXPERT = 2      # from this many (token, expert) pairs per expert on, every expert is computed for every token
 
 
-@FEED_FORWARDS.register("routed_mlp")
+@FEED_FORWARDS.register("mixture_of_experts")
 class RoutedMLP(FeedForward):
     graph_safe = True
 

@@ -97,6 +97,7 @@ class StateSpaceMixer(Mixer):
         self.dt_bias = _as_f32(tensors["dt_bias"])
         self.rate = torch.exp(_as_f32(tensors["A_log"]))
         self.skip = _as_f32(tensors["D"])
+        self.no_history = torch.empty((1, 0, self.channels), dtype=torch.float32, device=runtime.device)
 
     def forward(self, ctx, h, residual, run) -> None:
         self._run(ctx, h, residual, run, EPI_ACCUMULATE)
@@ -112,16 +113,14 @@ class StateSpaceMixer(Mixer):
         proj = ctx.rows("ssm.proj", 2 * inner + 2 * gn + self.n_heads)
         linear(h, self.w_in, proj, EPI_STORE)
         single = ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs
-        if self.taps > 1:
-            xbc = ctx.rows("ssm.xbc", self.channels)
-            ops.causal_conv(proj, inner, self.channels, self.conv_w, self.conv_b, run.entries[1], xbc, ctx.token_slot,
-                            ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs, single_tokens=single)
-        else:
-            raise RuntimeError("a state-space mixer without a convolution is not built")
+        xbc = ctx.rows("ssm.xbc", self.channels)
+        kept = run.entries[1] if self.taps > 1 else self.no_history      # one tap: a factor and a bias, nothing is kept
+        ops.causal_conv(proj, inner, self.channels, self.conv_w, self.conv_b, kept, xbc, ctx.token_slot,
+                        ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs, single_tokens=single)
         y = ctx.rows("ssm.y", inner, torch.float32)
         ops.decay_scan(xbc, inner + gn, inner, xbc, 0, proj, 2 * inner + 2 * gn, y, state, ctx.cu_seqlens, ctx.seq_slot,
                        ctx.n_seqs, self.n_heads, self.state, self.vdim, self.n_heads // self.groups, ops.DECAY_STEP,
-                       self.dt_bias, rate=self.rate, skip=self.skip, few_tokens=ctx.max_seq_tokens == 1,
+                       self.dt_bias, rate=self.rate, skip=self.skip, few_tokens=ctx.max_seq_tokens == 1, single_tokens=single,
                        **_chunking(ctx, self.n_heads * self.state * self.vdim, self.n_heads * self.state))
         g = ctx.rows("ssm.gated", inner)
         ops.gated_group_norm(y, proj[:, :inner], self.norm, self.eps, g, self.norm_groups, gate_first=True)
@@ -184,6 +183,7 @@ class GatedLinearAttention(Mixer):
         ops.decay_scan(proj, 0, qk, proj, 2 * qk, z, 0, o, state, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
                        self.n_heads, self.dim, self.vdim, 1, ops.DECAY_SIGMOID, self.a_bias, q_scale=self.dim ** -0.5,
                        inv_tau=1.0 / self.tau, few_tokens=ctx.max_seq_tokens == 1,
+                       single_tokens=ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs,
                        **_chunking(ctx, self.n_heads * self.dim * self.vdim, self.n_heads * self.dim))
         y = ctx.rows("gla.y", vv)
         ops.gated_group_norm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.eps, y, self.n_heads, gate_first=False)

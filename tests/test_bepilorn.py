@@ -75,6 +75,15 @@ def test_config_refuses_by_key(path, value, names):
     assert names in str(e.value)
 
 
+def test_a_layer_without_feed_forward_ignores_stray_norms_and_one_tap_is_a_convolution():
+    spec = describe_model(BP_ODD)
+    assert set(spec.ignored_names) == {"l1.norm2", "l1.norm2b"}
+    cfg = _changed(("layers", 0, "mixer", "conv"), 1)
+    from builderforce_inference_b200.parts.base import BLOCKS
+    need = BLOCKS.build(describe_model(cfg).layers[0].block).mixer().cache_need()
+    assert need == (StateNeed((3, 12, 8), "float32"),)             # nothing is kept for the convolution
+
+
 def test_model_as_data_names_every_tensor_with_its_shape():
     for cfg in (BP_ODD, BP_WIDE):
         want = {n: s for n, (s, _) in tensor_shapes(cfg).items()}

@@ -264,7 +264,8 @@ def scan(o, mode, dt, qk, v, raw, bias, rate, skip, seqs, state, H, D, V, hpg, q
                    "chunk_decay": torch.full((n_chunks, H * D), float("nan"), dtype=F32, device=DEV)}
     o.decay_scan(qk.to(dt).to(DEV), offs[0], offs[1], v.to(dt).to(DEV), offs[2], raw.to(dt).to(DEV), offs[3], out, state,
                  i32(cu), i32([s for s, _ in seqs]), len(seqs), H, D, V, hpg, mode, f(bias), rate=f(rate), skip=f(skip),
-                 q_scale=q_scale, inv_tau=inv_tau, few_tokens=max(t for _, t in seqs) == 1, **chunked)
+                 q_scale=q_scale, inv_tau=inv_tau, few_tokens=max(t for _, t in seqs) == 1,
+                 single_tokens=all(t == 1 for _, t in seqs), **chunked)
     return out.double().cpu()
 
 
@@ -371,7 +372,7 @@ def test_state_space_recurrence_with_groups_steps_and_skip(dt, H, G, N, Pd, scan
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
-@pytest.mark.parametrize("taps,C", [(2, 5), (3, 130), (4, 64), (5, 33)])
+@pytest.mark.parametrize("taps,C", [(1, 7), (2, 5), (3, 130), (4, 64), (5, 33)])
 def test_causal_convolution_over_portions_single_tokens_and_reused_slots(dt, taps, C):
     o = ops()
     g = torch.Generator().manual_seed(taps * 7 + C)
@@ -413,7 +414,8 @@ def test_causal_convolution_over_portions_single_tokens_and_reused_slots(dt, tap
         outs.append(run([(3, a[i:i + 1]), (1, c[i - at:i - at + 1])], single=True)[:1])
     assert rel_err(torch.cat(outs), ref_a) < t
     _, hist = plain(a)
-    assert rel_err(state[3], hist) < 1e-6
+    if taps > 1:
+        assert rel_err(state[3], hist) < 1e-6
     # slot 2 is given back and used again: its state is cleared by the cache; here by hand
     state[2].zero_()
     assert rel_err(run([(2, c)]), ref_c) < t
