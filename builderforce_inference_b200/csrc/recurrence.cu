@@ -279,16 +279,21 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
             step_c = rec_softplus(to_f32(nstep) + bias_h);
             w_h = expf(-rate_h * step_c);
         }
+        __align__(16) float tq[R], tk[R], ta[R];
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int d = lane * R + i;
             float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(to_f32(nr[i]) + bias_r[i]) * a.inv_tau);
             if (d >= D) w = 1.0f;
             if (PHASE != 0) prod[i] *= w;
-            qs[d] = d < D ? to_f32(nq[i]) * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f) : 0.0f;
-            ks[d] = d < D ? to_f32(nk[i]) : 0.0f;
-            as[d] = w;
+            tq[i] = d < D ? to_f32(nq[i]) * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f) : 0.0f;
+            tk[i] = d < D ? to_f32(nk[i]) : 0.0f;
+            ta[i] = w;
         }
+        // a lane's R neighbours go out as one store each
+        rec_load_rows<float, R>(tq, *reinterpret_cast<float(*)[R]>(qs + lane * R));
+        if (PHASE != 3) rec_load_rows<float, R>(tk, *reinterpret_cast<float(*)[R]>(ks + lane * R));
+        if (MODE == REC_DECAY_SIGMOID && PHASE != 3) rec_load_rows<float, R>(ta, *reinterpret_cast<float(*)[R]>(as + lane * R));
         const float old = nold;
         const float vv = to_f32(nv);
         __syncwarp();
