@@ -347,11 +347,11 @@ def bepilorn_config(width, heads, kv, d, ff, layers):
     ssm = {"heads": heads, "vdim": d, "state": d, "groups": kv, "conv": 4, "norm_groups": kv}
     pair = {"left": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": DESIGN_WINDOW},
                      "rot": {"base": 1e6, "dims": d // 2}},
-            "right": {"heads": heads, "dim": d, "vdim": d, "tau": 16.0, "rank": 64}, "left_scale": 0.6, "right_scale": 1.1}
+            "right": {"heads": heads, "dim": d, "vdim": d, "tau": 8.0, "rank": 64}, "left_scale": 0.5, "right_scale": 1.0}
     expert_ff = ff // 6 // 128 * 128            # a sixth of the dense inner size, in whole tiles
     mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": ff - 4 * expert_ff},
            "router": {"experts": BEPILORN_EXPERTS, "top": 4, "groups": {"count": 4, "keep": 2}}}
-    return {"architecture": "Bepilorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.25,
+    return {"architecture": "Bepilorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
             "layers": [{"type": "parallel" if i % 4 == 3 else "mamba2", "mixer": pair if i % 4 == 3 else ssm, "mlp": mlp}
                        for i in range(layers)]}
 
@@ -428,7 +428,8 @@ def kernel_run(a) -> int:
     ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
     ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``
     (``--seqs N``: N prompts of --rows tokens each),
-    ``--kernel qk_norm_rope --rows T``, ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
+    ``--kernel qk_norm_rope --rows T``, ``--kernel decay_scan --rows T [--seqs N]`` / ``--kernel decay_step --rows B`` (the
+    recurrence with a step size per head over prompts / over single tokens), ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
     matrix read once through the few-row products' TMA rings and nothing else: the floor under
     them).  Weights rotate over enough copies to exceed L2.  Prints one JSON line."""
     import torch
@@ -492,6 +493,38 @@ def kernel_run(a) -> int:
         # per token and head: scores and their use within a chunk (causal half of 64 x 64), q S and the state update
         flops = n_seq * t_new * h * (2.0 * d * d * 2 + (2.0 * 32 * (d + d) if chunks else 0.0))
         what = {"seqs": n_seq, "new_tokens": t_new, "heads": h, "dim": d, "vdim": d}
+    elif a.kernel in ("decay_scan", "decay_step"):
+        # the recurrence with a step size per head (state-space form): --seqs prompts of --rows tokens (chunked from 192
+        # tokens on), or --rows sequences of one token
+        from builderforce_inference_b200.kernels import ops
+        c = CONFIG_4B
+        h, g, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        prompt = a.kernel == "decay_scan"
+        n_seq, t_new = (a.seqs, a.rows) if prompt else (a.rows, 1)
+        n = n_seq * t_new
+        copies = 1 if prompt else max(2, int(400e6 // (n_seq * h * d * d * 4)) + 1)
+        bc = torch.randn(n, 2 * g * d, device=dev, dtype=torch.bfloat16)
+        x = torch.randn(n, h * d, device=dev, dtype=torch.bfloat16)
+        raw = torch.randn(n, h, device=dev, dtype=torch.bfloat16)
+        o = torch.empty(n, h * d, device=dev, dtype=torch.float32)
+        states = [torch.zeros(n_seq, h, d, d, device=dev, dtype=torch.float32) for _ in range(copies)]
+        bias, rate, skip = (torch.rand(h, device=dev) + 0.5 for _ in range(3))
+        cu = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+        chunked = {}
+        if prompt and t_new >= 192:
+            n_chunks = n // 64 + n_seq
+            chunked = {"chunk_len": 64, "max_chunks": (t_new + 63) // 64,
+                       "chunk_state": torch.empty(n_chunks, h * d * d, device=dev), "chunk_decay": torch.empty(n_chunks, h * d, device=dev)}
+
+        def one(i):
+            ops.decay_scan(bc, g * d, 0, x, 0, raw, 0, o, states[i % copies], cu, slots, n_seq, h, d, d, h // g, ops.DECAY_STEP, bias,
+                           rate=rate, skip=skip, few_tokens=not prompt, single_tokens=not prompt, **chunked)
+        bytes_moved = n_seq * h * d * d * 4 * 2 + n * ((2 * g * d + h * d + h) * 2 + h * d * 4)
+        # per token and state element: the update (multiply, multiply-add) and the output's multiply-add; chunked, the
+        # earlier tokens' part of the output once more
+        flops = n * h * d * d * (7.0 if chunked else 5.0)
+        what = {"seqs": n_seq, "new_tokens": t_new, "heads": h, "groups": g, "dim": d, "vdim": d, "chunked": bool(chunked)}
     elif a.kernel == "qk_prepare":
         # bias, row norm, adjacent-pair rotation over half a head, keys as values, cache write of one prompt of --rows tokens
         from builderforce_inference_b200.cache import KVView
@@ -718,7 +751,7 @@ def main() -> int:
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "weight_stream", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05", "lightning_chunks", "lightning_scan",
-                                                       "qk_prepare"],
+                                                       "qk_prepare", "decay_scan", "decay_step"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")

@@ -49,7 +49,7 @@ def moe(experts, top, ff, count=None, keep=None, shared=None):
 BP_ODD = {"architecture": "Bepilorn", "vocab": 131, "width": 40, "norm": {"eps": 2e-5}, "logit_scale": 0.7,
           "layers": [
               {"type": "mamba2", "mixer": ssm(3, 8, 12, 1, 2, 1), "mlp": moe(6, 3, 24, 3, 2, 40)},
-              {"type": "parallel", "mixer": par(soft(4, 2, 24, 10, 0.21, 9, (5000.0, 12)), gla(3, 8, 20, 4.0, 5), 0.6, 1.3),
+              {"type": "parallel", "mixer": par(soft(4, 2, 24, 10, 0.21, 9, (5000.0, 12)), gla(3, 8, 20, 4.0, 5), 0.7, 1.3),
                "mlp": None},
               {"type": "mamba2", "mixer": ssm(4, 6, 5, 2, 5, 3), "mlp": moe(5, 1, 16)},
               {"type": "parallel", "mixer": par(soft(3, 3, 16, 28, 0.3, 70, (100.0, 16)), gla(2, 24, 8, 32.0, 3), -0.8, 0.5),
@@ -59,9 +59,9 @@ BP_ODD = {"architecture": "Bepilorn", "vocab": 131, "width": 40, "norm": {"eps":
 # sizes nearer to a served model's: heads of 64, a state of 64, chunks of 128
 BP_WIDE = {"architecture": "Bepilorn", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
            "layers": [
-               {"type": "mamba2", "mixer": ssm(4, 64, 64, 2, 4, 2), "mlp": moe(8, 2, 64, 4, 2, 96)},
-               {"type": "parallel", "mixer": par(soft(8, 2, 64, 64, 0.11, 128, (1e4, 32)), gla(2, 64, 64, 16.0, 16), 0.5, 1.5),
-                "mlp": moe(8, 2, 64, 2, 1, 64)},
+               {"type": "mamba2", "mixer": ssm(6, 64, 64, 3, 4, 2), "mlp": moe(8, 2, 64, 4, 2, 128)},
+               {"type": "parallel", "mixer": par(soft(8, 2, 64, 64, 0.11, 128, (1e4, 32)), gla(2, 64, 64, 12.0, 8), 0.5, 1.5),
+                "mlp": moe(12, 3, 48, 3, 2, 64)},
                {"type": "mamba2", "mixer": ssm(2, 32, 128, 1, 4, 1), "mlp": None}]}
 CONFIGS = {"odd": BP_ODD, "wide": BP_WIDE}
 

@@ -29,7 +29,7 @@ def test_config_reads_every_size_and_constant():
     assert (p.left.heads, p.left.kv_heads, p.left.dim, p.left.vdim, p.left.scale, p.left.chunk) == (4, 2, 24, 10, 0.21, 9)
     assert (p.left.rot_base, p.left.rot_dims) == (5000.0, 12)
     assert (p.right.heads, p.right.dim, p.right.vdim, p.right.tau, p.right.rank) == (3, 8, 20, 4.0, 5)
-    assert (p.left_scale, p.right_scale) == (0.6, 1.3)
+    assert (p.left_scale, p.right_scale) == (0.7, 1.3)
     assert c.layers[1].mlp is None
     f = c.layers[0].mlp
     assert (f.experts, f.top, f.ff, f.groups, f.keep, f.shared_ff) == (6, 3, 24, 3, 2, 40)

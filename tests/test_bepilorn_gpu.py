@@ -115,7 +115,7 @@ def run_paged(q, pages, seqs, n_q, dv, scale, dt, sink):
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
-@pytest.mark.parametrize("n_q,n_kv,d,dv,chunk", [(4, 2, 24, 10, 9), (6, 1, 64, 32, 70), (3, 3, 16, 40, None), (2, 2, 32, 128, 64),
+@pytest.mark.parametrize("n_q,n_kv,d,dv,chunk", [(4, 2, 24, 10, 9), (6, 3, 64, 24, 70), (3, 3, 16, 40, None), (2, 2, 32, 128, 64),
                                                  (8, 2, 64, 64, 128)])
 def test_chunked_sink_attention_kernel_in_a_mixed_batch(dt, n_q, n_kv, d, dv, chunk):
     g = torch.Generator().manual_seed(n_q * 100 + d)
@@ -461,7 +461,7 @@ def test_sublayer_output_kernels():
 # ------------------------------------------------------------------------------------------------
 # the routed feed-forward
 # ------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("E,top,groups,keep", [(8, 2, 2, 1), (6, 3, 3, 2), (5, 1, 1, 1), (64, 6, 8, 3), (40, 8, 1, 1)])
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 2, 3, 1), (6, 3, 3, 2), (5, 1, 1, 1), (64, 6, 8, 3), (40, 8, 1, 1)])
 def test_router_against_the_plain_router(E, top, groups, keep):
     o = ops()
     g = torch.Generator().manual_seed(E + top)
