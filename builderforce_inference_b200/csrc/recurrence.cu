@@ -152,29 +152,15 @@ __global__ void decay_scan_kernel(const T* __restrict__ qk, const T* __restrict_
         for (int j = threadIdx.x; j < D; j += blockDim.x) chunk_decay[(chunk_no * a.H + h) * D + j] = ps[j];
 }
 
-// The same three phases with the state in registers, for D up to 128: a warp owns 32 columns of one
-// head of one sequence (or chunk), lane l holds all D rows of column v0 + l, so a token's output
-// value is one thread's sum and the warp never waits for another.  The lanes share the work of
-// fetching the token's q, k and decay input (lane l fetches rows l R .. l R + R - 1, one token ahead
-// of the arithmetic) and of evaluating the decay, and pass them to each other through the warp's own
-// piece of shared memory.
+// The same three phases with the state in registers, for D up to 128: a block of four warps owns up to
+// 128 columns of one head of one sequence (or chunk), a warp 32 of them, and lane l of a warp holds all
+// D rows of its column, so a token's output value is one thread's sum (four partial sums).  The block
+// shares the work on a token's q, k and decay: thread i fetches row i (one token ahead of the
+// arithmetic, kept in its storage type until used), evaluates the row's decay and puts the three values
+// into one of two buffers in shared memory, which all warps then read; with two buffers one barrier a
+// token is enough (whoever writes token t + 1 has passed the barrier of token t, which nobody reaches
+// before it has finished reading token t - 1).
 #define REC_WARPS 4
-
-// R neighbouring values of storage type T by one load; p is aligned to R * sizeof(T) bytes
-template <typename T, int R>
-__device__ __forceinline__ void rec_load_rows(const T* __restrict__ p, T (&dst)[R]) {
-    constexpr int BYTES = sizeof(T) * R;
-    if constexpr (BYTES == 16) {
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(p);
-    } else if constexpr (BYTES == 8) {
-        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p);
-    } else if constexpr (BYTES == 4) {
-        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(p);
-    } else {
-#pragma unroll
-        for (int i = 0; i < R; ++i) dst[i] = p[i];
-    }
-}
 
 template <typename T, int PHASE, int MODE, int DMAX>
 __global__ void __launch_bounds__(REC_WARPS * 32)
@@ -182,17 +168,16 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
                        float* __restrict__ out, float* __restrict__ state, float* __restrict__ chunk_state,
                        float* __restrict__ chunk_decay, const RecArgs a) {
     pdl_trigger();
-    constexpr int R = DMAX / 32;                   // rows a lane fetches
-    __shared__ __align__(16) float stage[REC_WARPS][3][DMAX];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int unit = blockIdx.x * REC_WARPS + warp;
+    __shared__ __align__(16) float stage[2][3][DMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
     const int seq = blockIdx.y;
     const int slot = a.seq_slot[seq];
-    if (slot < 0 || unit >= a.H * a.v_blocks) return;
+    if (slot < 0) return;
     const int D = a.D, V = a.V;
-    const int h = unit / a.v_blocks;
-    const int col = (unit - h * a.v_blocks) * 32 + lane;
+    const int h = blockIdx.x / a.v_blocks;                      // v_blocks: groups of 128 columns
+    const int col = (blockIdx.x - h * a.v_blocks) * (REC_WARPS * 32) + warp * 32 + lane;
     const bool col_ok = col < V;
+    const bool warp_ok = col - lane < V;                        // the warp has a column at all
     int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
     size_t chunk_no = 0;
     if (PHASE != 0) {
@@ -206,9 +191,6 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
     }
     const int grp = h / a.heads_per_group;
     const float skip = a.skip ? a.skip[h] : 0.0f;
-    float* qs = stage[warp][0];
-    float* ks = stage[warp][1];
-    float* as = stage[warp][2];
     float* sp = PHASE == 0 ? state + (((size_t)slot * a.H + h) * D) * V + col
                            : chunk_state + ((chunk_no * a.H + h) * D) * V + col;
     float S[DMAX];
@@ -221,83 +203,51 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
 #pragma unroll
         for (int d = 0; d < DMAX; ++d) S[d] = (PHASE == 3 && col_ok && d < D) ? sp[(size_t)d * V] : 0.0f;
     }
-    // the decay's constants of this lane's rows (rows lane * R .. lane * R + R - 1), and the running
-    // product of the chunk's decays
-    float bias_r[R], prod[R];
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int d = lane * R + i;
-        bias_r[i] = (MODE == REC_DECAY_SIGMOID && d < D) ? a.bias[(size_t)h * D + d] : 0.0f;
-        prod[i] = 1.0f;
-    }
+    // this thread's row (threads past DMAX have none), its decay's constant and the running product
+    // of the chunk's decays
+    const bool row_mine = tid < DMAX, row_ok = tid < D;
+    const float bias_r = (MODE == REC_DECAY_SIGMOID && row_ok) ? a.bias[(size_t)h * D + tid] : 0.0f;
     const float bias_h = MODE == REC_DECAY_STEP ? a.bias[h] : 0.0f;
     const float rate_h = MODE == REC_DECAY_STEP ? a.rate[h] : 0.0f;
-    // a lane's R rows are R neighbours in memory: one load each for q, k and the decay input where
-    // every token's rows are aligned to it (and D is whole lanes' worth), single values otherwise
-    const size_t vec_bytes = sizeof(T) * R;
-    const bool vec = R > 1 && D % R == 0 && a.qk_stride % R == 0 && a.r_stride % R == 0 && a.q_off % R == 0 && a.k_off % R == 0 &&
-                     a.r_off % R == 0 && ((uintptr_t)qk % vec_bytes) == 0 && ((uintptr_t)raw % vec_bytes) == 0;
-    // the next token's inputs stay as they were fetched (storage type) until they are used, so the
-    // loads are in flight while this token's arithmetic runs
-    __align__(16) T nq[R];
-    __align__(16) T nk[R];
-    __align__(16) T nr[R];
-    T nv = from_f32<T>(0.0f), nstep = from_f32<T>(0.0f);
+    float prod = 1.0f;
+    T nq = from_f32<T>(0.0f), nk = nq, nr = nq, nv = nq, nstep = nq;
     float nold = 0.0f;
     auto fetch = [&](int t) {
         const size_t tok = (size_t)(t0 + t);
         const T* row = qk + tok * a.qk_stride + (size_t)grp * D;
         const T* rr = raw + tok * a.r_stride + a.r_off;
-        const int d0 = lane * R;
-        if (vec) {
-            if (d0 < D) {
-                rec_load_rows<T, R>(row + a.q_off + d0, nq);
-                if (PHASE != 3) rec_load_rows<T, R>(row + a.k_off + d0, nk);
-                if (MODE == REC_DECAY_SIGMOID) rec_load_rows<T, R>(rr + (size_t)h * D + d0, nr);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int d = d0 + i;
-                if (d < D) {
-                    nq[i] = row[a.q_off + d];
-                    if (PHASE != 3) nk[i] = row[a.k_off + d];
-                    if (MODE == REC_DECAY_SIGMOID) nr[i] = rr[(size_t)h * D + d];
-                }
-            }
+        if (row_ok) {
+            nq = row[a.q_off + tid];
+            if (PHASE != 3) nk = row[a.k_off + tid];
+            if (MODE == REC_DECAY_SIGMOID) nr = rr[(size_t)h * D + tid];
         }
         if (MODE == REC_DECAY_STEP) nstep = rr[h];
         if (PHASE != 3 && col_ok) nv = vsrc[tok * a.v_stride + a.v_off + (size_t)h * V + col];
         if (PHASE == 3 && col_ok) nold = out[tok * a.out_stride + (size_t)h * V + col];
     };
-#pragma unroll
-    for (int i = 0; i < R; ++i) nq[i] = nk[i] = nr[i] = from_f32<T>(0.0f);
     if (nt > 0) fetch(0);
     for (int t = 0; t < nt; ++t) {
+        float* qs = stage[t & 1][0];
+        float* ks = stage[t & 1][1];
+        float* as = stage[t & 1][2];
         float step_c = 1.0f, w_h = 1.0f;
         if (MODE == REC_DECAY_STEP) {
             step_c = rec_softplus(to_f32(nstep) + bias_h);
             w_h = expf(-rate_h * step_c);
         }
-        __align__(16) float tq[R], tk[R], ta[R];
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int d = lane * R + i;
-            float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(to_f32(nr[i]) + bias_r[i]) * a.inv_tau);
-            if (d >= D) w = 1.0f;
-            if (PHASE != 0) prod[i] *= w;
-            tq[i] = d < D ? to_f32(nq[i]) * a.q_scale * (PHASE == 3 ? prod[i] : 1.0f) : 0.0f;
-            tk[i] = d < D ? to_f32(nk[i]) : 0.0f;
-            ta[i] = w;
+        if (row_mine) {
+            float w = MODE == REC_DECAY_STEP ? w_h : expf(rec_log_sigmoid(to_f32(nr) + bias_r) * a.inv_tau);
+            if (!row_ok) w = 1.0f;
+            if (PHASE != 0) prod *= w;
+            qs[tid] = row_ok ? to_f32(nq) * a.q_scale * (PHASE == 3 ? prod : 1.0f) : 0.0f;
+            if (PHASE != 3) ks[tid] = row_ok ? to_f32(nk) : 0.0f;
+            if (MODE == REC_DECAY_SIGMOID && PHASE != 3) as[tid] = w;
         }
-        // a lane's R neighbours go out as one store each
-        rec_load_rows<float, R>(tq, *reinterpret_cast<float(*)[R]>(qs + lane * R));
-        if (PHASE != 3) rec_load_rows<float, R>(tk, *reinterpret_cast<float(*)[R]>(ks + lane * R));
-        if (MODE == REC_DECAY_SIGMOID && PHASE != 3) rec_load_rows<float, R>(ta, *reinterpret_cast<float(*)[R]>(as + lane * R));
         const float old = nold;
         const float vv = to_f32(nv);
-        __syncwarp();
+        __syncthreads();
         if (t + 1 < nt) fetch(t + 1);
+        if (!warp_ok) continue;
         const float cv = step_c * vv;
         // four partial sums, so that a token's sum is four chains of D / 4 dependent operations
         float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
@@ -326,25 +276,18 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
             if (PHASE == 3) *dst = old + acc;
             else *dst = fmaf(skip, vv, acc);
         }
-        __syncwarp();
     }
     if (PHASE != 3 && col_ok) {
 #pragma unroll
         for (int d = 0; d < DMAX; ++d)
             if (d < D) sp[(size_t)d * V] = S[d];
     }
-    if (PHASE == 1 && unit == h * a.v_blocks) {
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            const int d = lane * R + i;
-            if (d < D) chunk_decay[(chunk_no * a.H + h) * D + d] = prod[i];
-        }
-    }
+    if (PHASE == 1 && blockIdx.x == h * a.v_blocks && row_ok) chunk_decay[(chunk_no * a.H + h) * D + tid] = prod;
 }
 
 // One new token per sequence: the state never rests anywhere.  A warp owns 32 columns of one head of
 // one sequence and streams the rows of its columns through once: read, decay, add, multiply by q, write.
-// The rows are asked for eight at a time so that a step's traffic, which is the states read and
+// The rows are asked for sixteen at a time so that a step's traffic, which is the states read and
 // written once, streams.
 #define REC_STEP_DMAX 512
 template <typename T, int MODE>
@@ -389,12 +332,12 @@ decay_step_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, const T*
     const float cv = step_c * vv;
     float acc0 = 0.0f, acc1 = 0.0f;
     int d = 0;
-    for (; d + 8 <= D; d += 8) {
-        float sv[8];
+    for (; d + 16 <= D; d += 16) {
+        float sv[16];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sv[i] = sp[(size_t)(d + i) * V];
+        for (int i = 0; i < 16; ++i) sv[i] = sp[(size_t)(d + i) * V];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 16; ++i) {
             sv[i] = fmaf(as[d + i], sv[i], ks[d + i] * cv);
             sp[(size_t)(d + i) * V] = sv[i];
             if (i & 1) acc1 = fmaf(sv[i], qs[d + i], acc1);
@@ -484,7 +427,7 @@ static int launch_decay_scan(const void* qk, const void* vsrc, const void* raw, 
 template <typename T, int MODE, int DMAX>
 static void launch_regs_phases(const void* qk, const void* vsrc, const void* raw, float* out, float* state, float* chunk_state,
                                float* chunk_decay, const RecArgs& a, int n_seqs, int max_chunks, cudaStream_t stream) {
-    const dim3 grid((a.H * a.v_blocks + REC_WARPS - 1) / REC_WARPS, n_seqs, max_chunks > 0 ? max_chunks : 1), block(REC_WARPS * 32);
+    const dim3 grid(a.H * a.v_blocks, n_seqs, max_chunks > 0 ? max_chunks : 1), block(REC_WARPS * 32);
     if (max_chunks <= 0) {
         bfi_launch(decay_scan_regs_kernel<T, 0, MODE, DMAX>, grid, block, 0, stream, (const T*)qk, (const T*)vsrc, (const T*)raw, out,
                    state, chunk_state, chunk_decay, a);
@@ -503,7 +446,7 @@ template <typename T>
 static int launch_decay_scan_regs(const void* qk, const void* vsrc, const void* raw, float* out, float* state,
                                   float* chunk_state, float* chunk_decay, RecArgs a, int n_seqs, int max_chunks,
                                   cudaStream_t stream) {
-    a.vb = 32, a.v_blocks = (a.V + 31) / 32;
+    a.vb = REC_WARPS * 32, a.v_blocks = (a.V + REC_WARPS * 32 - 1) / (REC_WARPS * 32);     // a block per 128 columns
 #define BFI_REC_REGS(M, DM) \
     launch_regs_phases<T, M, DM>(qk, vsrc, raw, out, state, chunk_state, chunk_decay, a, n_seqs, max_chunks, stream)
     if (a.mode == REC_DECAY_STEP) {
