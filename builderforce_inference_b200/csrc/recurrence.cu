@@ -251,22 +251,27 @@ decay_scan_regs_kernel(const T* __restrict__ qk, const T* __restrict__ vsrc, con
         const float cv = step_c * vv;
         // four partial sums, so that a token's sum is four chains of D / 4 dependent operations
         float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+        // rows past D hold q = k = 0, a = 1 and a zero state, so whole groups of 16 rows are walked
+        // and only groups that start past D are skipped
 #pragma unroll
-        for (int d4 = 0; d4 < DMAX; d4 += 4) {
-            if (d4 < D) {
-                const float4 q4 = *reinterpret_cast<const float4*>(qs + d4);
-                if (PHASE == 3) {
-                    acc0 = fmaf(S[d4], q4.x, acc0), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
-                    acc2 = fmaf(S[d4 + 2], q4.z, acc2), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
-                } else {
-                    const float4 k4 = *reinterpret_cast<const float4*>(ks + d4);
-                    float4 a4;
-                    if (MODE == REC_DECAY_STEP) a4 = make_float4(w_h, w_h, w_h, w_h);
-                    else a4 = *reinterpret_cast<const float4*>(as + d4);
-                    S[d4] = fmaf(a4.x, S[d4], k4.x * cv), acc0 = fmaf(S[d4], q4.x, acc0);
-                    S[d4 + 1] = fmaf(a4.y, S[d4 + 1], k4.y * cv), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
-                    S[d4 + 2] = fmaf(a4.z, S[d4 + 2], k4.z * cv), acc2 = fmaf(S[d4 + 2], q4.z, acc2);
-                    S[d4 + 3] = fmaf(a4.w, S[d4 + 3], k4.w * cv), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
+        for (int d16 = 0; d16 < DMAX; d16 += 16) {
+            if (d16 < D) {
+#pragma unroll
+                for (int d4 = d16; d4 < d16 + 16; d4 += 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + d4);
+                    if (PHASE == 3) {
+                        acc0 = fmaf(S[d4], q4.x, acc0), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
+                        acc2 = fmaf(S[d4 + 2], q4.z, acc2), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
+                    } else {
+                        const float4 k4 = *reinterpret_cast<const float4*>(ks + d4);
+                        float4 a4;
+                        if (MODE == REC_DECAY_STEP) a4 = make_float4(w_h, w_h, w_h, w_h);
+                        else a4 = *reinterpret_cast<const float4*>(as + d4);
+                        S[d4] = fmaf(a4.x, S[d4], k4.x * cv), acc0 = fmaf(S[d4], q4.x, acc0);
+                        S[d4 + 1] = fmaf(a4.y, S[d4 + 1], k4.y * cv), acc1 = fmaf(S[d4 + 1], q4.y, acc1);
+                        S[d4 + 2] = fmaf(a4.z, S[d4 + 2], k4.z * cv), acc2 = fmaf(S[d4 + 2], q4.z, acc2);
+                        S[d4 + 3] = fmaf(a4.w, S[d4 + 3], k4.w * cv), acc3 = fmaf(S[d4 + 3], q4.w, acc3);
+                    }
                 }
             }
         }
