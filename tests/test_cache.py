@@ -116,6 +116,45 @@ def test_window_group_lets_go_of_pages_behind_the_window():
     c.check()
 
 
+def test_chunked_group_with_values_of_their_own_size():
+    """A need whose tokens read only their own chunk of positions gives pages back behind the chunk,
+    and one whose values have another size than its keys keeps a value tensor of that size."""
+    c = make(needs=[KVNeed(2, 16, v_dim=40, chunk=100), KVNeed(2, 16), (KVNeed(2, 16, v_dim=40, chunk=100), StateNeed((3, 5)))],
+             max_tokens=64 * 16, max_seq_len=1024)
+    assert len(c.kv_groups) == 2
+    chunked = next(g for g in c.kv_groups if g.need.chunk == 100)
+    full = next(g for g in c.kv_groups if g.need.chunk is None)
+    assert chunked.runs == [0, 2] and chunked.bytes_per_token() == 2 * 2 * (16 + 40) * 4
+    view = c.run_cache(2).kv
+    assert view.k.shape == (16, 2, PAGE_TOKENS, 16) and view.v.shape == (16, 2, PAGE_TOKENS, 40)
+    assert (view.value_dim, view.chunk, view.plain) == (40, 100, False) and c.run_cache(1).kv.plain
+    assert c.run_cache(2).state.shape == (4, 3, 5) and len(c.run_cache(2).entries) == 2
+    s = c.acquire()
+    c.begin_step([s], [250])
+    assert chunked.table.held_pages() == 4     # the whole prompt is present during its step
+    c.end_step([s], [250])
+    # the next token, at 250, reads 200..250: page 3 only
+    assert chunked.table.held_pages() == 1 and full.table.held_pages() == 4
+    assert chunked.block_host[s, :4].tolist()[:3] == [-1, -1, -1]
+    for _ in range(50):
+        c.begin_step([s], [1]); c.end_step([s], [1])
+    # length 300: a new chunk starts with the next token, nothing before 300 is read again
+    assert chunked.table.held_pages() == 1 and chunked.table.first_kept_position(300) == 300
+    assert c.live_kv_bytes() == 300 * full.bytes_per_token() + 0 * chunked.bytes_per_token()
+    with pytest.raises(CacheError, match="rewind unsupported"):      # the fixed-size state speaks first
+        c.rewind(s, 10)
+    only = make(needs=[KVNeed(1, 16, chunk=100)], max_tokens=64 * 8, max_seq_len=512)
+    s2 = only.acquire()
+    only.begin_step([s2], [130]); only.end_step([s2], [130])
+    with pytest.raises(CacheError, match="chunks of 100"):
+        only.rewind(s2, 10)
+    c.poison()
+    assert torch.isnan(view.v).all() and torch.isnan(view.k).all()
+    c.release(s)
+    assert chunked.table.held_pages() == 0
+    c.check()
+
+
 def test_groups_and_shared_caches():
     needs = [KVNeed(2, 16), KVNeed(2, 16), KVNeed(2, 16, window=8), StateNeed((3, 5)), None, KVNeed(2, 16)]
     cache_of = [None, None, None, None, None, 1]
