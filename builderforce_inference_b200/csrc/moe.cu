@@ -20,6 +20,8 @@
 // When most experts are used anyway (many tokens), the dense products compute every expert for every
 // token on the tensor cores and bfi_moe_weigh_dense multiplies the activations by the chosen experts'
 // weights (0 for the others) between the two products:  act[t, e ff + j] *= weight of e for token t.
+// An expert that every token uses may stand behind the routed ones in both matrices (`tail` more
+// activations per token); its activations are multiplied by the token's gate.
 #include "common.cuh"
 
 __device__ __forceinline__ float moe_sigmoid(float x) {
@@ -302,7 +304,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ idx,
                 const float* __restrict__ weight, const int* __restrict__ token_slot, const float* __restrict__ shared_out,
                 long shared_stride, const float* __restrict__ gate, float* __restrict__ out, long out_stride, int top,
-                int width, int ff, int n_experts, int cols_per_block, int accumulate) {
+                int width, int ff, long ld, int cols_per_block, int accumulate) {
     pdl_trigger();
     extern __shared__ __align__(16) float as[];    // [top][ff]
     const int t = blockIdx.x;
@@ -318,7 +320,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
         float sum = 0.0f;
         for (int k = 0; k < top; ++k) {
             const int e = idx[(size_t)t * top + k];
-            const float d = warp_dot<T>(w_down + (size_t)c * n_experts * ff + (size_t)e * ff, as + (size_t)k * ff, ff, lane);
+            const float d = warp_dot<T>(w_down + (size_t)c * ld + (size_t)e * ff, as + (size_t)k * ff, ff, lane);
             sum = fmaf(weight[(size_t)t * top + k], d, sum);
         }
         if (lane == 0) {
@@ -331,7 +333,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
 
 extern "C" int bfi_moe_down(const void* act, int dtype, const void* w_down, const int* idx, const float* weight,
                             const int* token_slot, const float* shared_out, long shared_stride, const float* gate,
-                            float* out, long out_stride, int n_tokens, int top, int width, int ff, int n_experts,
+                            float* out, long out_stride, int n_tokens, int top, int width, int ff, long ld,
                             int accumulate, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_down: unknown dtype code %d", dtype);
     BFI_REQUIRE(top > 0 && width > 0 && ff > 0 && out_stride >= width, "moe_down: bad sizes");
@@ -350,24 +352,24 @@ extern "C" int bfi_moe_down(const void* act, int dtype, const void* w_down, cons
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_down_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_down_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)act, (const float*)w_down, idx,
-                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, n_experts, cols_per_block,
+                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, ld, cols_per_block,
                        accumulate);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_down_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_down_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)act, (const bf16*)w_down, idx,
-                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, n_experts, cols_per_block,
+                       weight, token_slot, shared_out, shared_stride, gate, out, out_stride, top, width, ff, ld, cols_per_block,
                        accumulate);
     }
     if (e != cudaSuccess) return bfi_fail("moe_down: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     return bfi_check_launch("moe_down");
 }
 
-// one block per token; act [tokens][E * ff]
+// one block per token; act [tokens][E * ff + tail]
 template <typename T>
 __global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, const int* __restrict__ idx,
                                        const float* __restrict__ weight, const int* __restrict__ token_slot, int top, int E,
-                                       int ff) {
+                                       int ff, int tail, const float* __restrict__ gate) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float comb[];                // [E] the token's weight of every expert
@@ -382,22 +384,28 @@ __global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, con
         const float c = comb[j / ff];
         row[j] = c == 0.0f ? from_f32<T>(0.0f) : from_f32<T>(to_f32(row[j]) * c);
     }
+    if (tail > 0 && gate != nullptr) {
+        const float g = gate[t];
+        for (int j = E * ff + threadIdx.x; j < E * ff + tail; j += blockDim.x) row[j] = from_f32<T>(to_f32(row[j]) * g);
+    }
 }
 
 extern "C" int bfi_moe_weigh_dense(void* act, long act_stride, int dtype, const int* idx, const float* weight,
-                                   const int* token_slot, int n_tokens, int top, int E, int ff, cudaStream_t stream) {
+                                   const int* token_slot, int n_tokens, int top, int E, int ff, int tail, const float* gate,
+                                   cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_weigh_dense: unknown dtype code %d", dtype);
-    BFI_REQUIRE(top > 0 && top <= 1024 && E > 0 && ff > 0 && act_stride >= (long)E * ff, "moe_weigh_dense: bad sizes");
+    BFI_REQUIRE(top > 0 && top <= 1024 && E > 0 && ff > 0 && tail >= 0 && act_stride >= (long)E * ff + tail,
+                "moe_weigh_dense: bad sizes");
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)E * sizeof(float);
     BFI_REQUIRE(smem <= 48 * 1024, "moe_weigh_dense: %d experts are too many for this kernel", E);
     const int threads = top > 256 ? 1024 : 256;
     if (dtype == BFI_F32)
         bfi_launch(moe_weigh_dense_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (float*)act, act_stride, idx, weight,
-                   token_slot, top, E, ff);
+                   token_slot, top, E, ff, tail, gate);
     else
         bfi_launch(moe_weigh_dense_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, stream, (bf16*)act, act_stride, idx, weight,
-                   token_slot, top, E, ff);
+                   token_slot, top, E, ff, tail, gate);
     return bfi_check_launch("moe_weigh_dense");
 }
 

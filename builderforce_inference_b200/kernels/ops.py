@@ -561,13 +561,15 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, n_experts: int, idx: torch
              gate: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
     """``out[t] (= | +=) sum_k weight[t, k] * down_e act[t, k] + gate[t] * shared_out[t]`` with
     ``e = idx[t, k]`` (the last term only with ``shared_out``; ``gate`` None is 1); ``w_down`` is
-    ``[width, experts * ff]`` with expert e's columns at ``e ff``, ``out`` float32 ``[tokens, width]``."""
+    ``[width, experts * ff]`` with expert e's columns at ``e ff`` (its rows may be further apart: the
+    first columns of a wider matrix), ``out`` float32 ``[tokens, width]``."""
     _need_cuda(act, w_down, idx, weight, token_slot, out, shared_out, gate)
     _rows_2d(out, "feed-forward output")
+    _rows_2d(w_down, "expert down matrices")
     n, top = idx.shape
     width, ff = w_down.shape[0], w_down.shape[1] // n_experts
-    if w_down.dim() != 2 or w_down.shape[1] != n_experts * ff or not w_down.is_contiguous() or w_down.dtype != act.dtype:
-        raise KernelError("moe_down: expert weights must be contiguous [width, experts * ff] of the activations' dtype")
+    if w_down.shape[1] != n_experts * ff or w_down.dtype != act.dtype:
+        raise KernelError("moe_down: expert weights must be [width, experts * ff] of the activations' dtype")
     if not act.is_contiguous() or act.shape != (n * top, ff):
         raise KernelError("moe_down: the activations must be contiguous [tokens * top, ff]")
     if out.dtype != torch.float32 or out.shape != (n, width):
@@ -577,24 +579,28 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, n_experts: int, idx: torch
     library("core").call("bfi_moe_down", _ptr(act), c_int(dtype_code(act.dtype)), _ptr(w_down), _ptr(idx), _ptr(weight),
                          _ptr(token_slot), _ptr(shared_out), c_long(0 if shared_out is None else shared_out.stride(0)),
                          _ptr(gate), _ptr(out), c_long(out.stride(0)), c_int(n), c_int(top), c_int(width), c_int(ff),
-                         c_int(n_experts), c_int(1 if accumulate else 0), _stream())
+                         c_long(w_down.stride(0)), c_int(1 if accumulate else 0), _stream())
 
 
 def moe_weigh_dense(act: torch.Tensor, n_experts: int, idx: torch.Tensor, weight: torch.Tensor,
-                    token_slot: torch.Tensor) -> None:
+                    token_slot: torch.Tensor, tail: int = 0, gate: Optional[torch.Tensor] = None) -> None:
     """``act[t, e ff + j] *= (weight of expert e for token t, 0 if it was not chosen)`` over
-    activations ``[tokens, experts * ff]`` that the dense product computed for every expert."""
-    _need_cuda(act, idx, weight, token_slot)
+    activations ``[tokens, experts * ff + tail]`` that the dense product computed for every expert;
+    the last ``tail`` columns (an expert every token uses) are multiplied by ``gate[t]``."""
+    _need_cuda(act, idx, weight, token_slot, gate)
     _rows_2d(act, "dense expert activations")
     _i32(idx, "expert choices")
     _i32(token_slot, "token slots")
     n, top = idx.shape
-    if act.shape[0] != n or act.shape[1] % n_experts != 0 or weight.dtype != torch.float32 or not weight.is_contiguous() \
-            or weight.shape != (n, top):
-        raise KernelError("moe_weigh_dense: activations [tokens, experts * ff], weights float32 [tokens, top]")
+    routed = act.shape[1] - tail
+    if act.shape[0] != n or tail < 0 or routed <= 0 or routed % n_experts != 0 or weight.dtype != torch.float32 \
+            or not weight.is_contiguous() or weight.shape != (n, top):
+        raise KernelError("moe_weigh_dense: activations [tokens, experts * ff + tail], weights float32 [tokens, top]")
+    if tail and (gate is None or gate.dtype != torch.float32 or not gate.is_contiguous() or gate.numel() < n):
+        raise KernelError("moe_weigh_dense: the tail needs one float32 gate per token")
     library("core").call("bfi_moe_weigh_dense", _ptr(act), c_long(act.stride(0)), c_int(dtype_code(act.dtype)), _ptr(idx),
-                         _ptr(weight), _ptr(token_slot), c_int(n), c_int(top), c_int(n_experts),
-                         c_int(act.shape[1] // n_experts), _stream())
+                         _ptr(weight), _ptr(token_slot), c_int(n), c_int(top), c_int(n_experts), c_int(routed // n_experts),
+                         c_int(tail), _ptr(gate), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:

@@ -16,8 +16,10 @@ matrices side by side), which serve two ways of computing: a step with few (toke
 reads only the chosen experts' weights (``kernels/ops.moe_gate_up``, ``moe_down``); a bfloat16 step
 with at least ``DENSE_PAIRS_PER_EXPERT`` pairs per expert, which touches nearly every expert anyway,
 runs the two dense products over all experts on the tensor cores and multiplies the activations by
-the chosen experts' weights, 0 for the others, in between (``moe_weigh_dense``).  The shared expert
-runs through the dense products.  Nothing here reads a choice back to the host, so a step through
+the chosen experts' weights, 0 for the others, in between (``moe_weigh_dense``); the shared expert
+stands behind the routed ones in both matrices and is weighed by its gate there, so the dense way is
+two products and one kernel between them.  In the other way the shared expert runs through dense
+products of its own.  Nothing here reads a choice back to the host, so a step through
 this part can be captured in a graph.
 """
 from __future__ import annotations
@@ -72,16 +74,24 @@ class RoutedMLP(FeedForward):
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
         gu = [torch.stack([mats[3 * e], mats[3 * e + 1]], dim=1).reshape(2 * self.inner, self.width) for e in range(self.n_experts)]
-        self.w_gu = torch.cat(gu, dim=0).contiguous()                                         # [E * 2 * ff, width]
-        self.w_down = torch.cat([mats[3 * e + 2] for e in range(self.n_experts)], dim=1).contiguous()   # [width, E * ff]
+        downs = [mats[3 * e + 2] for e in range(self.n_experts)]
         rows = [tensors["router"].float()]
         if self.shared_inner is not None:
+            # the shared expert stands behind the routed ones in both matrices, so the dense way is two
+            # products for all of them; the other way reads it through views (and its own down matrix)
             rows.append(tensors["shared.gate"].float())
-            g, u = tensors["shared.gate_proj"], tensors["shared.up_proj"]
-            if g.dtype != u.dtype:
-                g, u = g.float(), u.float()
-            self.ws_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.shared_inner, self.width).contiguous()
-            self.ws_down = tensors["shared.down_proj"]
+            g, u, dn = tensors["shared.gate_proj"], tensors["shared.up_proj"], tensors["shared.down_proj"]
+            if len({g.dtype, u.dtype, dn.dtype, gu[0].dtype}) > 1:
+                g, u, dn, gu, downs = g.float(), u.float(), dn.float(), [m.float() for m in gu], [m.float() for m in downs]
+            gu.append(torch.stack([g, u], dim=1).reshape(2 * self.shared_inner, self.width))
+            downs.append(dn)
+            self.ws_down = dn.contiguous()
+        self.w_gu_all = torch.cat(gu, dim=0).contiguous()                  # [(E * ff + shared) * 2, width]
+        self.w_down_all = torch.cat(downs, dim=1).contiguous()             # [width, E * ff + shared]
+        routed = self.n_experts * self.inner
+        self.w_gu = self.w_gu_all[:2 * routed]                             # [E * 2 * ff, width]
+        self.w_down = self.w_down_all[:, :routed]                          # [width, E * ff], rows of the wider matrix
+        self.routed_rows = 2 * routed                                      # the shared expert's gate/up rows follow
         self.w_router = torch.cat(rows, dim=0).contiguous()          # float32: the product runs on the CUDA cores
         self.correction = tensors["correction"].float().contiguous() if self.has_correction else None
 
@@ -99,23 +109,20 @@ class RoutedMLP(FeedForward):
         gate = ctx.rows("moe.gate", 1, torch.float32).view(-1) if shared else None
         ops.moe_router(h, self.w_router, self.n_experts, self.correction, ctx.token_slot, idx, wts, self.top, self.n_groups,
                        self.keep_groups, self.weight_scale, gate)
+        if h.dtype == torch.bfloat16 and self.w_gu_all.dtype == torch.bfloat16 \
+                and n * self.top >= DENSE_PAIRS_PER_EXPERT * self.n_experts:
+            tail = self.shared_inner or 0
+            act = ctx.rows("moe.act.dense", self.n_experts * self.inner + tail)
+            linear(h, self.w_gu_all, act, EPI_SWIGLU)
+            ops.moe_weigh_dense(act, self.n_experts, idx, wts, ctx.token_slot, tail, gate)
+            linear(act, self.w_down_all, target, EPI_ACCUMULATE if accumulate else EPI_STORE)
+            return
         ys = None
         if shared:
             act_s = ctx.rows("moe.shared.act", self.shared_inner)
-            linear(h, self.ws_gate_up, act_s, EPI_SWIGLU)
+            linear(h, self.w_gu_all[self.routed_rows:], act_s, EPI_SWIGLU)
             ys = ctx.rows("moe.shared.out", self.width, torch.float32)
             linear(act_s, self.ws_down, ys, EPI_STORE)
-        if h.dtype == torch.bfloat16 and self.w_gu.dtype == torch.bfloat16 \
-                and n * self.top >= DENSE_PAIRS_PER_EXPERT * self.n_experts:
-            act = ctx.rows("moe.act.dense", self.n_experts * self.inner)
-            linear(h, self.w_gu, act, EPI_SWIGLU)
-            ops.moe_weigh_dense(act, self.n_experts, idx, wts, ctx.token_slot)
-            if shared:      # gate * shared output first, then the experts' sum on top
-                ops.gated_rows(target, ys, gate, accumulate)
-                linear(act, self.w_down, target, EPI_ACCUMULATE)
-            else:
-                linear(act, self.w_down, target, EPI_ACCUMULATE if accumulate else EPI_STORE)
-            return
         act = ctx.rows("moe.act", self.top * self.inner).view(n * self.top, self.inner)
         ops.moe_gate_up(h, self.w_gu, self.n_experts, idx, ctx.token_slot, act)
         ops.moe_down(act, self.w_down, self.n_experts, idx, wts, ctx.token_slot, target, ys, gate, accumulate)

@@ -197,6 +197,35 @@ def test_one_loud_key_just_inside_and_just_outside_the_chunk(dt, chunk):
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
+def test_one_loud_key_far_back_among_hundreds_and_the_first_tokens(dt):
+    """Without a chunk every earlier key is read: a loud key at position 3 decides the output of a query
+    400 positions on (in a prompt, as a continuation over a page border and as a single token), and the
+    first three tokens, which come before it, do not hear it."""
+    n_q, n_kv, d, dv, n, loud = 3, 1, 24, 12, 404, 3
+    g = torch.Generator().manual_seed(17)
+    k = 0.05 * torch.randn(n, n_kv, d, generator=g)
+    v = 0.05 * torch.randn(n, n_kv, dv, generator=g)
+    q = 0.05 * torch.randn(n, n_q, d, generator=g)
+    k[loud, 0, 0], q[:, :, 0], v[loud, 0, :] = 40.0, 40.0, 7.0
+    sink = torch.tensor([0.0, -1.0, 2.0])
+    pages = Pages(3, n + 60, n_kv, d, dv, dt)
+    for slot in range(3):
+        pages.write(slot, 0, k, v)
+    kk, vv = pages.read(0, n)
+    ref = P.chunk_sink_attention(q64(q, dt), kk, vv, 0.25, None, sink.double()).reshape(n, n_q * dv)
+    t = 1e-5 if dt == F32 else 2e-2
+    whole = run_paged(q.reshape(n, -1), pages, [(0, 0, n)], n_q, dv, 0.25, dt, sink)
+    assert rel_err(whole, ref) < t
+    assert float(whole[:loud].abs().max()) < 1.0 and float(whole[loud:, 0].min()) > 3.0
+    rest = run_paged(q[380:].reshape(n - 380, -1), pages, [(1, 380, n - 380)], n_q, dv, 0.25, dt, sink)
+    assert rel_err(rest, ref[380:]) < t
+    one = run_paged(q[n - 1:].reshape(1, -1), pages, [(2, n - 1, 1)], n_q, dv, 0.25, dt, sink)
+    assert rel_err(one, ref[n - 1:]) < t and float(one[0, 0]) > 3.0
+    first = run_paged(q[:1].reshape(1, -1), pages, [(2, 0, 1)], n_q, dv, 0.25, dt, sink)
+    assert rel_err(first, ref[:1]) < t
+
+
+@pytest.mark.parametrize("dt", [F32, BF16])
 def test_a_sink_per_head_takes_the_weight_of_its_head_only(dt):
     n_q, n_kv, d, dv, n = 4, 2, 8, 4, 70
     g = torch.Generator().manual_seed(3)
@@ -521,12 +550,18 @@ def test_expert_products_read_the_chosen_experts(dt, width, ff, E, top):
     acc = torch.full((n, width), 5.0, dtype=F32, device=DEV)
     o.moe_down(act, w_dn, E, idx.to(DEV), wt.to(DEV), i32(slots), acc, accumulate=True)
     # the dense way's weighing: every expert's activations times the token's weight of it, 0 where it was not chosen
-    dense = torch.ones(n, E * ff, dtype=dt, device=DEV)
-    o.moe_weigh_dense(dense, E, idx.to(DEV), wt.to(DEV), i32(slots))
+    dense = torch.ones(n, E * ff + 5, dtype=dt, device=DEV)             # five more columns: an expert every token uses
+    o.moe_weigh_dense(dense, E, idx.to(DEV), wt.to(DEV), i32(slots), 5, gate.to(DEV))
     comb = torch.zeros(n, E, dtype=P.F)
     comb.scatter_(1, idx.long(), wt.double())
     keep_rows = [t for t in range(n) if t != 4]
-    assert rel_err(dense.cpu()[keep_rows], q64(comb.repeat_interleave(ff, dim=1), dt)[keep_rows]) < 1e-6
+    want = torch.cat([comb.repeat_interleave(ff, dim=1), gate.double()[:, None].expand(n, 5)], dim=1)
+    assert rel_err(dense.cpu()[keep_rows], q64(want, dt)[keep_rows]) < 1e-6
+    # the down matrices as the first columns of a wider matrix
+    wide = torch.cat([w_dn, torch.full((width, 9), float("nan"), dtype=dt, device=DEV)], dim=1)
+    out2 = torch.full((n, width), 5.0, dtype=F32, device=DEV)
+    o.moe_down(act, wide[:, :E * ff], E, idx.to(DEV), wt.to(DEV), i32(slots), out2, shared.to(DEV), gate.to(DEV))
+    assert rel_err(out2.cpu()[keep_rows], out.cpu()[keep_rows]) < 1e-5      # rows that are not 16-byte aligned sum in another order
     g_out = torch.full((n, width), 2.0, dtype=F32, device=DEV)
     o.gated_rows(g_out, shared.to(DEV), gate.to(DEV), accumulate=True)
     assert rel_err(g_out, 2.0 + gate.double()[:, None] * shared.double()) < 1e-6
