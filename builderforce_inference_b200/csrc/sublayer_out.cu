@@ -2,6 +2,8 @@
 // than add it: a norm of the output before the add, and a weighted sum of two outputs.
 //
 //   bfi_norm_add:      x[t, :] += y[t, :] * rsqrt(mean(y[t, :]^2) + eps) * w        (y float32)
+//                      and, when asked, the next sublayer's norm of the new x in the same kernel:
+//                      h[t, :] = x[t, :] * rsqrt(mean(x[t, :]^2) + eps2) * w2       (h in the activation dtype)
 //   bfi_weighted_sum:  out[t, :] = a * y0[t, :] + b * y1[t, :]                      (all float32)
 //   bfi_scale_rows:    x[r, :] *= s                                                 (float32)
 //   bfi_gated_rows:    out[r, :] (= | +=) g[r] * src[r, :]                          (float32)
@@ -11,7 +13,8 @@
 #include "common.cuh"
 
 __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride,
-                                const void* __restrict__ w, int w_dtype, int width, float eps) {
+                                const void* __restrict__ w, int w_dtype, int width, float eps, const void* __restrict__ w2,
+                                int w2_dtype, float eps2, void* __restrict__ h, int h_dtype, long h_stride) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[33];
@@ -22,17 +25,31 @@ __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const floa
     for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int j = threadIdx.x; j < width; j += blockDim.x) xr[j] += yr[j] * scale * load_as_f32(w, w_dtype, j);
+    float ss2 = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = xr[j] + yr[j] * scale * load_as_f32(w, w_dtype, j);
+        xr[j] = v;
+        ss2 = fmaf(v, v, ss2);
+    }
+    if (h == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float scale2 = 1.0f / sqrtf(ss2 / (float)width + eps2);
+    // every thread reads back the values it wrote itself
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        store_from_f32(h, h_dtype, (size_t)t * h_stride + j, xr[j] * scale2 * load_as_f32(w2, w2_dtype, j));
 }
 
 extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stride, const void* w, int w_dtype,
-                            int n_rows, int width, float eps, cudaStream_t stream) {
-    BFI_REQUIRE(dtype_ok(w_dtype), "norm_add: unknown dtype code %d", w_dtype);
+                            int n_rows, int width, float eps, const void* w2, int w2_dtype, float eps2, void* h,
+                            int h_dtype, long h_stride, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(w_dtype) && dtype_ok(w2_dtype) && dtype_ok(h_dtype), "norm_add: unknown dtype code");
     BFI_REQUIRE(n_rows >= 0 && width > 0, "norm_add: bad sizes rows=%d width=%d", n_rows, width);
     BFI_REQUIRE(x_stride >= width && y_stride >= width, "norm_add: row stride shorter than the row");
+    BFI_REQUIRE(h == nullptr || (w2 != nullptr && h_stride >= width), "norm_add: the next norm needs its weight and rows of the width");
     if (n_rows == 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps);
+    bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, w2,
+               w2_dtype, eps2, h, h_dtype, h_stride);
     return bfi_check_launch("norm_add");
 }
 

@@ -337,10 +337,18 @@ def _f32_vector(t: Optional[torch.Tensor], n: int, what: str) -> None:
         raise KernelError(f"{what} must be contiguous float32 [{n}] on the GPU")
 
 
-def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> None:
+def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, next_w: Optional[torch.Tensor] = None,
+             next_eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
     """``x[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w``: a sublayer's output, normed, into the
-    float32 residual stream."""
-    _need_cuda(x, y, w)
+    float32 residual stream.  With ``next_w`` and ``out`` the next sublayer's norm of the new ``x`` is
+    made in the same kernel: ``out[t] = x[t] * rsqrt(mean(x[t]^2) + next_eps) * next_w``."""
+    _need_cuda(x, y, w, next_w, out)
+    if (next_w is None) != (out is None):
+        raise KernelError("norm_add: the next norm needs both its weight and its output")
+    if out is not None:
+        _rows_2d(out, "norm output")
+        if out.shape != x.shape or next_w.shape != (x.shape[1],) or not next_w.is_contiguous():
+            raise KernelError("norm_add: the next norm's output must be [rows, width] and its weight [width]")
     _rows_2d(x, "residual stream")
     _rows_2d(y, "sublayer output")
     if x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape:
@@ -348,7 +356,10 @@ def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float) -> N
     if w.shape != (x.shape[1],) or not w.is_contiguous():
         raise KernelError(f"norm_add: weight must be [{x.shape[1]}]")
     library("core").call("bfi_norm_add", _ptr(x), c_long(x.stride(0)), _ptr(y), c_long(y.stride(0)), _ptr(w),
-                         c_int(dtype_code(w.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps), _stream())
+                         c_int(dtype_code(w.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps), _ptr(next_w),
+                         c_int(0 if next_w is None else dtype_code(next_w.dtype)), c_float(next_eps), _ptr(out),
+                         c_int(0 if out is None else dtype_code(out.dtype)), c_long(0 if out is None else out.stride(0)),
+                         _stream())
 
 
 def weighted_sum(out: torch.Tensor, y0: torch.Tensor, a: float, y1: torch.Tensor, b: float) -> None:

@@ -7,7 +7,8 @@ the mixer's and the feed-forward's last matrix product.
 ``sandwich``  a norm before and after each sublayer: ``x += norm1b(mixer(norm1(x)));
               x += norm2b(ffn(norm2(x)))``; the feed-forward (with its two norms) may be absent.
               The sublayers write their output to a float32 buffer (``forward_store``) and the
-              second norm adds it, normed, into the residual stream in one kernel.
+              second norm adds it, normed, into the residual stream in one kernel, which also makes
+              the feed-forward's input norm.
 """
 from __future__ import annotations
 
@@ -92,8 +93,9 @@ class SandwichBlock(Block):
         y = ctx.rows("sublayer.out", residual.shape[1], torch.float32)
         h = self.norm1.forward(ctx, residual)
         self._mixer.forward_store(ctx, h, y, run)
-        self.norm1b.add_to(ctx, residual, y)
-        if self.ffn is not None:
-            h = self.norm2.forward(ctx, residual)
-            self.ffn.forward_store(ctx, h, y)
-            self.norm2b.add_to(ctx, residual, y)
+        if self.ffn is None:
+            self.norm1b.add_to(ctx, residual, y)
+            return
+        h = self.norm1b.add_to(ctx, residual, y, then=self.norm2)      # the add and the next norm in one kernel
+        self.ffn.forward_store(ctx, h, y)
+        self.norm2b.add_to(ctx, residual, y)

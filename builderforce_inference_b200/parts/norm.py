@@ -35,6 +35,12 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
 
-    def add_to(self, ctx, residual, y) -> None:
-        """``residual += norm(y)``: both float32 ``[tokens, width]``."""
-        ops.norm_add(residual, y, self.weight, self.eps)
+    def add_to(self, ctx, residual, y, then=None):
+        """``residual += norm(y)``: both float32 ``[tokens, width]``.  With ``then`` (the norm that reads
+        the residual stream next) its output is made in the same kernel and returned."""
+        if not isinstance(then, RMSNorm):
+            ops.norm_add(residual, y, self.weight, self.eps)
+            return None if then is None else then.forward(ctx, residual)
+        out = ctx.rows("norm.out", then.width)
+        ops.norm_add(residual, y, self.weight, self.eps, next_w=then.weight, next_eps=then.eps, out=out)
+        return out

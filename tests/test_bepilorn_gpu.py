@@ -477,6 +477,13 @@ def test_sublayer_output_kernels():
     xd = x.to(DEV)
     o.norm_add(xd, y.to(DEV), w.to(DEV), 2e-5)
     assert rel_err(xd, x.double() + P.rms(y.double(), 2e-5) * w.double()) < 1e-6
+    # the same with the next norm of the new x in the same kernel
+    for dt in (F32, BF16):
+        xd2, w2 = x.to(DEV), (1.0 + 0.25 * torch.randn(40, generator=g))
+        hn = torch.full((6, 40), float("nan"), dtype=dt, device=DEV)
+        o.norm_add(xd2, y.to(DEV), w.to(DEV), 2e-5, next_w=w2.to(DEV), next_eps=3e-5, out=hn)
+        assert torch.equal(xd2, xd)
+        assert rel_err(hn, P.rms(xd.double().cpu(), 3e-5) * w2.double()) < (1e-6 if dt == F32 else 8e-3)
     out = torch.empty(6, 40, device=DEV)
     o.weighted_sum(out, y.to(DEV), -0.8, y2.to(DEV), 1.3)
     assert rel_err(out, -0.8 * y.double() + 1.3 * y2.double()) < 1e-6
