@@ -181,3 +181,45 @@ def model(name, dtype, seed=3):
 def prompts(vocab, lengths, seed=5):
     g = torch.Generator().manual_seed(seed)
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def _divisors(n):
+    return [d for d in range(1, n + 1) if n % d == 0]
+
+
+def random_config(seed):
+    """A configuration drawn from a seed: two to five layers in any order, sizes from lists that hold
+    odd ones and ones past what the register kernels take, chunks that are and are not whole pages,
+    routers with and without groups, layers with and without a feed-forward or a shared expert."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([48, 64, 96, 160, 256])
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        if rng.random() < 0.55:
+            heads, vdim = rng.choice([1, 2, 3, 4, 6, 8]), rng.choice([8, 16, 24, 32, 48, 64])
+            mixer = ssm(heads, vdim, rng.choice([4, 16, 48, 64, 96, 136]), rng.choice(_divisors(heads)), rng.choice([1, 2, 3, 4, 6]),
+                        rng.choice([g for g in _divisors(heads * vdim) if g <= 8]))
+            kind = "mamba2"
+        else:
+            heads = rng.choice([1, 2, 4, 6, 8])
+            kv, dim = rng.choice(_divisors(heads)), rng.choice([16, 32, 48, 64, 80, 128])
+            vdim, chunk = rng.choice([8, 16, 32, 64, 128, dim]), rng.choice([None, 7, 33, 64, 100, 128, 200])
+            rot = (rng.choice([100.0, 1e4, 5e5]), rng.choice(list(range(2, dim + 1, 2)))) if rng.random() < 0.8 else None
+            left = soft(heads, kv, dim, vdim, rng.choice([0.05, 0.125, dim ** -0.5, 0.3]), chunk, rot)
+            right = gla(rng.choice([1, 2, 3, 4]), rng.choice([8, 16, 48, 64, 144]), rng.choice([8, 16, 40, 64, 128]),
+                        rng.choice([1.0, 4.0, 16.0, 64.0]), rng.choice([4, 16, 24]))
+            mixer = par(left, right, rng.choice([0.3, 0.7, 1.0, -0.5]), rng.choice([0.4, 1.0, 1.7]))
+            kind = "parallel"
+        mlp = None
+        if rng.random() < 0.85:
+            experts = rng.choice([2, 4, 6, 8, 12, 16, 32])
+            count = rng.choice(_divisors(experts))
+            keep = rng.randint(1, count)
+            top = rng.randint(1, min(keep * (experts // count), 6))
+            mlp = moe(experts, top, rng.choice([8, 20, 32, 64, 72]), count if rng.random() < 0.8 else None, keep, rng.choice([None, 16, 40, 96]))
+            if "groups" not in mlp["router"]:
+                mlp["router"]["top"] = min(top, experts)
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Bepilorn", "vocab": rng.choice([97, 256, 333, 1000]), "width": width, "norm": {"eps": rng.choice([1e-6, 1e-5])},
+            "logit_scale": rng.choice([0.5, 1.0, 0.7]), "layers": layers}

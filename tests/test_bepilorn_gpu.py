@@ -10,7 +10,7 @@ import os
 import pytest
 import torch
 
-from bepilorn_models import BF16, CONFIGS, F32, model, prompts
+from bepilorn_models import BF16, CONFIGS, F32, make_weights, model, prompts, random_config, write_folder
 from helpers import rel_err
 from plain import bepilorn_plain as P
 
@@ -695,6 +695,51 @@ def test_batch_against_each_alone_in_float32():
         assert rel_err(nxt[i:i + 1], eng.step([S(sl, [7])])) < 1e-5
         eng.release(sl)
         at += len(s)
+
+
+@pytest.mark.parametrize("seed", range(101, 113))
+def test_random_configurations_in_float32(seed):
+    """Configurations drawn from a seed (layer order, every size, chunks, groups, with and without
+    feed-forward, shared expert and rotation): an unequal batch of prompts, five tokens decoded
+    together, and the longest prompt again in portions, against the plain implementation.  A prompt
+    whose routers decide by less than 1e-4 somewhere is not compared (a float32 sum may turn it)."""
+    from builderforce_inference_b200.engine.engine import Engine
+    cfg = random_config(seed)
+    w = make_weights(cfg, seed, F32)
+    eng = Engine.load(write_folder(cfg, w), dtype="float32", max_tokens=2048)
+    w64 = {k: v.to(torch.float64) for k, v in w.items()}
+    lens = [(1, 5, 70, 130, 260)[seed % 5], (2, 33, 200)[seed % 3], (1, 64, 129)[seed % 2]]
+    seqs = prompts(cfg["vocab"], [n + 5 for n in lens], seed)
+    refs, steady = [], []
+    for s in seqs:
+        rep = []
+        refs.append(P.forward(cfg, w64, s, None, rep))
+        steady.append(not rep or min(rep) > 1e-4)
+    slots = [eng.acquire() for _ in seqs]
+    got = eng.step([S(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)])
+    at = 0
+    for i, n in enumerate(lens):
+        if steady[i]:
+            assert rel_err(got[at:at + n], refs[i][:n]) < 4e-4, (i, cfg)
+        at += n
+    for step in range(5):
+        got = eng.step([S(sl, [s[n + step]]) for sl, s, n in zip(slots, seqs, lens)])
+        for i, n in enumerate(lens):
+            if steady[i]:
+                assert rel_err(got[i:i + 1], refs[i][n + step:n + step + 1]) < 4e-4, (i, step, cfg)
+    for sl in slots:
+        eng.release(sl)
+    i = max(range(3), key=lambda k: lens[k])
+    sl, outs, at = eng.acquire(), [], 0
+    for c in [max(1, lens[i] // 3), 2, 1, 97, 10 ** 6]:
+        c = min(c, lens[i] - at)
+        if c > 0:
+            outs.append(eng.step([S(sl, seqs[i][at:at + c])]).clone())
+            at += c
+    if steady[i]:
+        assert rel_err(torch.cat(outs), refs[i][:lens[i]]) < 4e-4, cfg
+    eng.release(sl)
+    eng.cache.check()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
