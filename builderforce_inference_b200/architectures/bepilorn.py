@@ -46,7 +46,7 @@ def bepilorn_spec(cfg: BepilornConfig) -> ModelSpec:
             left = PartSpec("attention", {
                 "width": cfg.width, "n_heads": a.heads, "n_kv_heads": a.kv_heads, "head_dim": a.dim, "v_dim": a.vdim,
                 "position": position, "eps": cfg.eps, "scale": a.scale, "chunk": a.chunk, "bias": True,
-                "out_bias": False, "sink": "learned"})
+                "out_bias": False, "sink": "learned", "exact_weights": True})
             right = PartSpec("gated_linear", {"width": cfg.width, "n_heads": g.heads, "dim": g.dim, "vdim": g.vdim,
                                               "tau": g.tau, "decay_rank": g.rank, "eps": cfg.eps})
             mixer = PartSpec("weighted_sum", {"members": {"left": left, "right": right},

@@ -19,7 +19,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv,
-                         int window, int chunk, float scale_log2, float sink_log2, const float* __restrict__ sinks) {
+                         int window, int chunk, float scale_log2, float sink_log2, const float* __restrict__ sinks,
+                         int split_p) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -188,11 +189,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
             // ---- output += P V, 16 keys at a time
 #pragma unroll
             for (int ks4 = 0; ks4 < 4; ++ks4) {
-                uint32_t pa[4];
+                uint32_t pa[4], pl[4];
                 pa[0] = pack_bf16(s[2 * ks4][0], s[2 * ks4][1]);
                 pa[1] = pack_bf16(s[2 * ks4][2], s[2 * ks4][3]);
                 pa[2] = pack_bf16(s[2 * ks4 + 1][0], s[2 * ks4 + 1][1]);
                 pa[3] = pack_bf16(s[2 * ks4 + 1][2], s[2 * ks4 + 1][3]);
+                if (split_p) {
+                    // the weights stay float32 in effect: what the rounding to bfloat16 left over is a
+                    // second bfloat16 term (16 bits of mantissa together) with a product of its own
+                    pl[0] = pack_bf16(s[2 * ks4][0] - bf16_lo(pa[0]), s[2 * ks4][1] - bf16_hi(pa[0]));
+                    pl[1] = pack_bf16(s[2 * ks4][2] - bf16_lo(pa[1]), s[2 * ks4][3] - bf16_hi(pa[1]));
+                    pl[2] = pack_bf16(s[2 * ks4 + 1][0] - bf16_lo(pa[2]), s[2 * ks4 + 1][1] - bf16_hi(pa[2]));
+                    pl[3] = pack_bf16(s[2 * ks4 + 1][2] - bf16_lo(pa[3]), s[2 * ks4 + 1][3] - bf16_hi(pa[3]));
+                }
 #pragma unroll
                 for (int dd = 0; dd < D / 8; dd += 2) {
                     uint32_t b[4];
@@ -200,6 +209,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                     ldmatrix_x4_trans(b, tile_chunk<D>(vt, row, dd + (lane >> 4)));
                     mma16816(o[dd], pa, b[0], b[1]);
                     mma16816(o[dd + 1], pa, b[2], b[3]);
+                    if (split_p) {
+                        mma16816(o[dd], pl, b[0], b[1]);
+                        mma16816(o[dd + 1], pl, b[2], b[3]);
+                    }
                 }
             }
         }
@@ -228,7 +241,8 @@ template <int D>
 static int launch_prefill(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                           const void* v_pages, const int* block_table, int table_stride, const int* cu_seqlens,
                           const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int n_q, int n_kv,
-                          int window, int chunk, float scale, float sink, const float* sinks, cudaStream_t stream) {
+                          int window, int chunk, float scale, float sink, const float* sinks, int split_p,
+                          cudaStream_t stream) {
     const size_t smem = (size_t)(AP_QROWS * D + 4 * AD_TILE * D) * sizeof(bf16);
     auto kernel = attention_prefill_kernel<D>;
     if (smem > 48 * 1024) {
@@ -239,7 +253,7 @@ static int launch_prefill(const void* q, long q_stride, void* out, long out_stri
     dim3 grid((max_tokens + AP_QROWS - 1) / AP_QROWS, n_q, n_seqs);
     bfi_launch(kernel, grid, dim3(AD_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, cu_seqlens, seq_slot, seq_start, n_q,
-               n_kv, window, chunk, scale * 1.4426950408889634f, sink * 1.4426950408889634f, sinks);
+               n_kv, window, chunk, scale * 1.4426950408889634f, sink * 1.4426950408889634f, sinks, split_p);
     return bfi_check_launch("attention_prefill");
 }
 
@@ -247,11 +261,13 @@ static int launch_prefill(const void* q, long q_stride, void* out, long out_stri
 // `sink`: a score beside the keys' whose exponential joins the softmax's denominator; -infinity for none;
 // `sinks` (float32, one per query head) takes its place when given.  `chunk` > 0: a token reads only
 // the keys of its own block of `chunk` consecutive positions, blocks counted from position 0.
+// `split_p`: the softmax's weights enter the second product as two bfloat16 terms (the rounded weight
+// and what the rounding left over), for designs whose attention weights are float32 by rule.
 extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                           const void* v_pages, const int* block_table, int table_stride,
                                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
                                           int max_tokens, int n_q, int n_kv, int d, int window, int chunk, float scale,
-                                          float sink, const float* sinks, cudaStream_t stream) {
+                                          float sink, const float* sinks, int split_p, cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && chunk >= 0, "attention_prefill: negative window or chunk");
@@ -262,7 +278,9 @@ extern "C" int bfi_attention_prefill_bf16(const void* q, long q_stride, void* ou
         return 2;
     if (d == 64)
         return launch_prefill<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, stream);
+                                  seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, split_p,
+                                  stream);
     return launch_prefill<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, cu_seqlens,
-                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, stream);
+                               seq_slot, seq_start, n_seqs, max_tokens, n_q, n_kv, window, chunk, scale, sink, sinks, split_p,
+                               stream);
 }

@@ -42,6 +42,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// the two bfloat16 values of a packed pair, as float32
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
 
 // A tile in shared memory: [64 rows][D] bfloat16; the 16-byte chunk c of row r sits at chunk
 // c ^ (r & 7), which makes the 8 row addresses of every ldmatrix fall into distinct banks.

@@ -228,8 +228,10 @@ def attention_decode_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n
     return attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale, probe=(spin_limit, hold_producer))
 
 
-def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sink=None) -> bool:
-    """Tensor-core attention for steps that bring more than one token per sequence."""
+def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sink=None,
+                           exact_weights: bool = False) -> bool:
+    """Tensor-core attention for steps that bring more than one token per sequence.
+    ``exact_weights``: the softmax's weights enter the second product as two bfloat16 terms."""
     d = kv.head_dim
     if d not in (64, 128) or kv.value_dim != d or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False
@@ -239,7 +241,7 @@ def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_head
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot),
         _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads),
         c_int(d), c_int(kv.window or 0), c_int(kv.chunk or 0), c_float(scale), _sink(None if sinks is not None else sink),
-        _ptr(sinks), _stream())
+        _ptr(sinks), c_int(1 if exact_weights else 0), _stream())
 
 
 TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles

@@ -19,6 +19,8 @@ denominator carries ``exp(sink)``; a number, or ``"learned"``: one per query hea
 checkpoint); ``v_dim`` (value heads of another size than the keys'); ``chunk`` (a token reads only
 the keys of its own block of ``chunk`` consecutive positions, blocks counted from position 0);
 ``out_bias`` (whether the output projection carries a bias when the others do; default: it does);
+``exact_weights`` (the softmax's weights stay float32 up to the second product, also in a bfloat16
+run: the tensor-core prompt kernel then multiplies with two bfloat16 terms per weight);
 the position encoding's pairing and partial width.  The plain
 combination (no bias, head norm or none, own values, rotate-half) runs the per-head kernel that
 fuses norm, rotation and cache write; the others run the per-token kernel that also adds the
@@ -44,7 +46,7 @@ class Attention(Mixer):
                  position: Optional[PartSpec] = None, qk_norm=False, eps: float = 1e-6,
                  window: Optional[int] = None, scale: Optional[float] = None, own_kv: bool = True,
                  bias: bool = False, values: str = "projection", sink=None, v_dim: Optional[int] = None,
-                 chunk: Optional[int] = None, out_bias: Optional[bool] = None):
+                 chunk: Optional[int] = None, out_bias: Optional[bool] = None, exact_weights: bool = False):
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"GQA: {n_heads} query heads do not divide into {n_kv_heads} kv heads")
         if head_dim % 2 != 0 or head_dim > 512:
@@ -71,7 +73,7 @@ class Attention(Mixer):
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.qk_norm, self.eps, self.window = (qk_norm or None), float(eps), window
         self.bias, self.values_are_keys = bool(bias), values == "keys"
-        self.v_dim, self.chunk = v_dim, chunk
+        self.v_dim, self.chunk, self.exact_weights = v_dim, chunk, bool(exact_weights)
         self.out_bias = self.bias if out_bias is None else bool(out_bias)
         if self.out_bias and not self.bias:
             raise ValueError("an output bias without the projections' biases is not a known variant")
@@ -194,7 +196,7 @@ class Attention(Mixer):
     def attend(self, ctx, qkv, out, kv) -> None:
         from ..kernels import attention as fast_attention
         sink = self.sinks if self.learned_sink else self.sink
-        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale, sink):
+        if fast_attention.attend(ctx, qkv, out, kv, self.n_heads, self.scale, sink, self.exact_weights):
             return
         ops.attention_paged(qkv, qkv.stride(0), out, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                             ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, sink)

@@ -162,6 +162,13 @@ def test_tensor_core_prompt_attention_with_chunks_and_a_sink_per_head(n_q, n_kv,
     assert choose.attend(ctx, qd, out, pages.view, n_q, 0.2, sink.float().to(DEV))
     assert library("fast").calls == before + 1
     assert rel_err(out, torch.cat(refs)) < 1.5e-2
+    # with the weights kept float32 in effect (two bfloat16 terms each) only the output's own rounding is left
+    exact = torch.full((qd.shape[0], n_q * d), float("nan"), dtype=BF16, device=DEV)
+    assert choose.attend(ctx, qd, exact, pages.view, n_q, 0.2, sink.float().to(DEV), exact_weights=True)
+    ref = torch.cat(refs)
+    err_exact = float((exact.double().cpu() - ref).abs().max())
+    assert err_exact <= float((out.double().cpu() - ref).abs().max()) + 1e-6
+    assert float((exact.double().cpu() - ref.to(BF16).double()).abs().max()) <= 2.0 * float(ref.abs().max()) * 2.0 ** -9
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
