@@ -92,7 +92,7 @@ class RoutedMLP(FeedForward):
         self.w_gu = self.w_gu_all[:2 * routed]                             # [E * 2 * ff, width]
         self.w_down = self.w_down_all[:, :routed]                          # [width, E * ff], rows of the wider matrix
         self.routed_rows = 2 * routed                                      # the shared expert's gate/up rows follow
-        self.w_router = torch.cat(rows, dim=0).contiguous()          # float32: the product runs on the CUDA cores
+        self.w_router = torch.cat(rows, dim=0).contiguous()                # float32: the logits are float32 sums
         self.correction = tensors["correction"].float().contiguous() if self.has_correction else None
 
     def forward_store(self, ctx, h, out) -> None:
